@@ -1,0 +1,331 @@
+#!/usr/bin/env python
+"""Benchmark of the EXL3 MoE expert path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--rows R] [--layers L] [--impl reference]
+
+Workload (N = 1, default): benchmark config 2 -- the MoE layer decoding ONE token (hidden 2048, 64 routed
+experts + 1 shared, top-4, SwiGLU experts 2048 -> 1536 -> 2048, all EXL3 4 bpw) -- walked over a stack of 47
+layers with distinct random weights (config 5's stack, 14.4 GB), so that every packed word comes from HBM
+(one layer's touched weights, 23.7 MB, would otherwise sit in the 126 MB L2).  One step = the token through
+all 47 layers (each layer with its own input row and routing table, as the stack is "experts only").
+    value   = layer-tokens per second = rows * layers / step time, inputs resident in HBM, the step replayed
+              as one CUDA graph, CUDA-event timed.
+    e2e     = the same through the host-buffer C-ABI call (glmflash_moe_run_host) per layer: pinned host
+              activations / picks / routing weights copied in, the layer output copied back, every step.
+    roofline= the dominant kernel (gate/up grouped GEMV + SwiGLU epilogue), launched alone over the stack and
+              timed with CUDA events: algorithmic bytes per launch / average duration / measured HBM peak.
+N > 1: the 64 routed experts are split evenly over the ranks (expert parallel), the shared expert goes round
+robin over the layers; each rank computes a partial layer output, NCCL all-gathers the partials over NVLink and
+every rank adds them in rank order (the reference's fixed-order sum after its all-gather).  Total work is fixed:
+"scaling": "strong".
+--impl reference: the reference's CPU path for the op (its scalar oracle restated in oracle/exl3_oracle.c; the
+Rust original cannot be built here) on all host threads, bounded samples of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as entry  # noqa: E402
+
+H, I, E, S = 2048, 1536, 64, 5
+MAT_BYTES = H * I // 2                                     # packed bytes of one matrix
+W_E = 3 * MAT_BYTES + (2 * H + 2 * I + I + H) * 2          # 4,740,096 B: one expert's matrices + its six scale vectors
+GATEUP_BYTES_E = 2 * MAT_BYTES + (2 * H + 3 * I) * 2       # what the gate/up kernel reads per expert (algorithmic)
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle samples while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
+            self.t.start()
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.t.join(timeout=2)
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def host_layer_inputs(synth, layers, rows, seed0=5000):
+    xs, ps, ws = [], [], []
+    for l in range(layers):
+        xs.append(synth.activations_bf16(seed0 + 3 * l, rows, H))
+        p, w = synth.route(seed0 + 3 * l + 1, rows, E, S - 1, shared_bias=rows > 1)
+        ps.append(p); ws.append(w)
+    return np.stack(xs), np.stack(ps), np.stack(ws)
+
+
+def cpu_sample(O, synth, rows, budget_s=12.0):
+    """The CPU baseline: the oracle's whole-layer path (unpack every touched matrix, fp32 dot products in the
+    reference's split/warp order, epilogues, combine) on all host threads, on layers of the same workload."""
+    threads = O.max_threads()
+    bank = synth.expert_bank(1000, H, I, E)
+    t0, n = time.time(), 0
+    while True:
+        x = synth.activations_bf16(7000 + n, rows, H)
+        picks, rw = synth.route(7100 + n, rows, E, S - 1, shared_bias=rows > 1)
+        Y = O.experts_run_rows(bank, H, I, E + 1, S, x, picks, mode=0, sk_gu=4, sk_dn=1, threads=threads)
+        O.combine(Y, rw, rows, S, H)
+        n += 1
+        if time.time() - t0 > budget_s or n >= 64:
+            break
+    dt = time.time() - t0
+    return rows * n / dt, threads, f"{n} layer passes of {rows} token(s), {dt:.1f} s"
+
+
+def run_reference(args, rank):
+    if rank != 0:
+        return
+    O = entry.load_oracle()
+    entry.load_package()
+    from glmflash_b200 import synth
+    threads = O.max_threads()
+    bank = synth.expert_bank(1000, H, I, E)
+    times = []
+    for i in range(args.warmup + args.steps):
+        x = synth.activations_bf16(7000 + i, args.rows, H)
+        picks, rw = synth.route(7100 + i, args.rows, E, S - 1, shared_bias=args.rows > 1)
+        t0 = time.time()
+        Y = O.experts_run_rows(bank, H, I, E + 1, S, x, picks, mode=0, sk_gu=4, sk_dn=1, threads=threads)
+        O.combine(Y, rw, args.rows, S, H)
+        if i >= args.warmup:
+            times.append(time.time() - t0)
+    ms = 1e3 * float(np.mean(times))
+    v = args.rows / (ms / 1e3)
+    sample = f"each step = 1 layer pass of {args.rows} token(s) of the {args.layers}-layer workload"
+    print(json.dumps({
+        "impl": "reference", "metric": "EXL3-4bpw MoE layer tok/s", "value": v, "unit": "layer-tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+        "config": workload_config(args),
+        "cpu_baseline": {"value": v, "unit": "layer-tokens/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "layer-tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def workload_config(args):
+    return {"workload": f"moe_layer_decode_bs{args.rows} (config 2{'/3' if args.rows > 1 else ''}) over a {args.layers}-layer stack of distinct "
+                        "weights (config 5 stack)", "hidden": H, "intermediate": I, "experts": E, "shared_experts": 1, "top_k": S - 1,
+            "bits_per_weight": 4, "rows": args.rows, "layers": args.layers,
+            "l2": f"weights of a step ({args.layers} layers) exceed L2; every layer has its own weights",
+            "parallelism": f"ep{args.gpus}"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--rows", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=47)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    pkg = entry.load_package()
+    from glmflash_b200 import synth
+    pkg.lib()                                                   # fails loudly when the CUDA library is missing
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node N for --gpus N"
+    G = world
+    R, L = args.rows, args.layers
+    assert E % G == 0
+
+    # ---- weights: one bank per layer, generated on the device (identical on every rank)
+    banks = [synth.device_bank(1000 * l + 1, H, I, E, dev) for l in range(L)]
+    structs = [pkg.weights_struct(b) for b in banks]
+    xs, ps, ws = host_layer_inputs(synth, L, R)
+    x_d = torch.from_numpy(xs.view(np.int16)).to(dev).view(torch.bfloat16)      # [L][R][H]
+    p_d = torch.from_numpy(ps).to(dev)
+    w_d = torch.from_numpy(ws).to(dev)
+
+    # ---- owners: expert window per rank; the shared expert goes round robin over the layers
+    lo, hi = rank * (E // G), (rank + 1) * (E // G)
+    moes = {}
+    for sh in ((0, 1) if G > 1 else (1,)):
+        moes[sh] = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=max(R, 1), shared_exl3=sh, expert_lo=lo, expert_hi=hi))
+    owner = lambda l: moes[1 if (G == 1 or l % G == rank) else 0]
+    if G > 1:
+        gathered = torch.empty((G, R, H), dtype=torch.float32, device=dev)
+        final = torch.empty((L, R, H), dtype=torch.float32, device=dev)
+
+    def layer(l):
+        m = owner(l)
+        m.run(structs[l], x_d[l], p_d[l], w_d[l], R)
+        if G > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
+            pkg.rank_sum(gathered, final[l])
+
+    def step_eager():
+        for l in range(L):
+            layer(l)
+
+    stream = torch.cuda.Stream()
+    graph = None
+    with torch.cuda.stream(stream):
+        step_eager()
+        stream.synchronize()
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                step_eager()
+            graph = g
+        except Exception as ex:                                  # NCCL capture can be refused: time eager launches
+            if rank == 0:
+                print(f"graph capture failed ({type(ex).__name__}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+    step = (lambda: graph.replay()) if graph is not None else step_eager
+
+    def timed(fn, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms / steps
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(step, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    value = R * L / (ms_step / 1e3)
+
+    # ---- end to end: pinned host buffers through the host-buffer C-ABI call, every layer, every step
+    xh = torch.from_numpy(xs.view(np.int16)).pin_memory()
+    ph, wh = torch.from_numpy(ps).pin_memory(), torch.from_numpy(ws).pin_memory()
+    oh = torch.empty((L, R, H), dtype=torch.float32).pin_memory()
+    part_h = torch.empty((R, H), dtype=torch.float32).pin_memory()
+
+    def step_e2e():
+        for l in range(L):
+            m = owner(l)
+            if G == 1:
+                m.run_host(structs[l], xh[l], ph[l], wh[l], R, oh[l], stream=stream)
+            else:                                                # partial on this rank, exchange, rank-ordered sum, read back
+                m.run_host(structs[l], xh[l], ph[l], wh[l], R, part_h, stream=stream)
+                dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
+                pkg.rank_sum(gathered, final[l], stream=stream)
+                oh[l].copy_(final[l], non_blocking=True)
+                stream.synchronize()
+    ms_e2e = timed(step_e2e, max(3, args.steps // 4), 3)
+    e2e = {"value": R * L / (ms_e2e / 1e3), "unit": "layer-tokens/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": L * (R * H * 2 + 2 * R * S * 4), "d2h_bytes_per_step": L * R * H * 4,
+           "call": "glmflash_moe_run_host per layer (pinned host input / picks / weights in, output out, sync)"}
+
+    # ---- roofline of the dominant kernel: gate/up GEMV alone, every layer, back to back (N = 1 only)
+    roofline = None
+    if G == 1:
+        m = moes[1]
+        peak, how = measured_peaks()
+        distinct = [len(np.unique(ps[l])) for l in range(L)]     # experts touched incl. the shared one
+        m.set_phases(4)                                          # gate/up only (scratch of the last step stays in place)
+
+        def gateup_pass():
+            for l in range(L):
+                m.run(structs[l], x_d[l], p_d[l], w_d[l], R)
+        ms_pass = timed(gateup_pass, max(5, args.steps), 3)
+        m.set_phases(31)
+        bytes_per_launch = float(np.mean(distinct)) * GATEUP_BYTES_E + R * H * 2 * 2
+        achieved = bytes_per_launch / (ms_pass / L * 1e-3) / 1e9
+        roofline = {"bound": "hbm", "kernel": "gemv_kernel<2,*> (gate/up grouped GEMV + SwiGLU epilogue)", "achieved": achieved,
+                    "peak": peak, "peak_source": how + " (MEASURED_PEAKS.json hbm_gbs)" if how == "measured" else how,
+                    "unit": "GB/s", "frac": achieved / peak, "us_per_launch": ms_pass / L * 1e3,
+                    "algorithmic_bytes_per_launch": bytes_per_launch, "traffic": None,
+                    "layer": {"algorithmic_bytes": float(np.mean(distinct)) * W_E + R * H * 6, "us": ms_step / L * 1e3,
+                              "gbs": (float(np.mean(distinct)) * W_E + R * H * 6) / (ms_step / L * 1e-3) / 1e9}}
+        roofline["layer"]["frac"] = roofline["layer"]["gbs"] / peak
+
+    cpu = None
+    if rank == 0 and G == 1 and not args.no_cpu_baseline:
+        O = entry.load_oracle()
+        v, cores, sample = cpu_sample(O, synth, R)
+        cpu = {"value": v, "unit": "layer-tokens/s", "cores": cores, "kind": "port", "sample": sample}
+
+    if rank == 0:
+        out = {"metric": "EXL3-4bpw MoE layer tok/s", "value": value, "unit": "layer-tokens/s", "n_gpus": G, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+               "dtype": "f16xf16->f32", "data": "synthetic", "config": workload_config(args),
+               "stack_tokens_per_s": R / (ms_step / 1e3), "graph": graph is not None,
+               "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * L * args.steps + (0 if G == 1 else L * args.steps),
+               "roofline": roofline, "cpu_baseline": cpu}
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,281 @@
+"""Host-side mirror of the reference operator surface over the C ABI (include/glmflash_b200.h).
+
+The reference's owners are Rust structs (`ExpertGpu` src/experts.rs:365, `FastExperts`
+src/fast_experts.rs:27, `Grouping` src/grouping.rs:12, `Moe` src/moe.rs:11); no Rust toolchain exists in this
+build environment, so the owners live in C++ behind the C ABI and this module binds them with ctypes for the
+tests and the benchmark.  torch is used only for device memory and streams.  There is no CPU fallback: every
+constructor raises when the CUDA library is missing or no GPU is present.
+"""
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+SO_PATH = os.path.join(_HERE, "libglmflash_b200.so")
+
+
+class Config(C.Structure):
+    _fields_ = [("hidden", C.c_int32), ("inter", C.c_int32), ("experts", C.c_int32), ("slots", C.c_int32),
+                ("max_rows", C.c_int32), ("shared_exl3", C.c_int32), ("expert_lo", C.c_int32),
+                ("expert_hi", C.c_int32), ("limit", C.c_float), ("reserved", C.c_int32 * 7)]
+
+
+class Weights(C.Structure):
+    _fields_ = [(n, C.c_void_p) for n in ("gt", "ut", "dt", "suh_g", "suh_u", "suh_d", "svh_g", "svh_u", "svh_d")]
+
+
+WEIGHT_NAMES = [n for n, _ in Weights._fields_]
+
+# every symbol include/glmflash_b200.h declares: name -> (restype, argtypes)
+_P, _I, _Z = C.c_void_p, C.c_int, C.c_size_t
+SYMBOLS = {
+    "glmflash_abi_version": (_I, []),
+    "glmflash_config_bytes": (_Z, []),
+    "glmflash_weights_bytes": (_Z, []),
+    "glmflash_error": (C.c_char_p, []),
+    "glmflash_exl3_decode": (_I, [_P, _P, C.c_int64, _P]),
+    "glmflash_exl3_linear_scratch_bytes": (_Z, [_I, _I]),
+    "glmflash_exl3_linear": (_I, [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P]),
+    "glmflash_grouping_new": (_I, [_P, _Z, _P]),
+    "glmflash_grouping_free": (None, [_P]),
+    "glmflash_grouping_run": (_I, [_P, _P, _P, _I]),
+    "glmflash_grouping_ids": (_P, [_P]),
+    "glmflash_grouping_count": (_P, [_P]),
+    "glmflash_grouping_members": (_P, [_P]),
+    "glmflash_experts_new": (_I, [_P, _Z, _P]),
+    "glmflash_experts_free": (None, [_P]),
+    "glmflash_experts_run_rows": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I]),
+    "glmflash_experts_y": (_P, [_P]),
+    "glmflash_experts_xd": (_P, [_P]),
+    "glmflash_experts_status": (_P, [_P]),
+    "glmflash_experts_set_phases": (_I, [_P, _I]),
+    "glmflash_fast_experts_new": (_I, [_P, _Z, _P]),
+    "glmflash_fast_experts_free": (None, [_P]),
+    "glmflash_fast_experts_run": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I]),
+    "glmflash_fast_experts_output": (_P, [_P]),
+    "glmflash_fast_experts_xd": (_P, [_P]),
+    "glmflash_moe_new": (_I, [_P, _Z, _P]),
+    "glmflash_moe_free": (None, [_P]),
+    "glmflash_moe_run": (_I, [_P, _P, _P, _P, _I, _P, _P, _I]),
+    "glmflash_moe_output": (_P, [_P]),
+    "glmflash_moe_set_phases": (_I, [_P, _I]),
+    "glmflash_moe_run_host": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _P]),
+    "glmflash_rank_sum": (_I, [_P, _P, _I, _I, _I, _P]),
+}
+
+_lib = None
+
+
+class GlmFlashError(RuntimeError):
+    pass
+
+
+def lib():
+    """The loaded C-ABI library.  Raises when it has not been built: there is no other path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(SO_PATH):
+            raise GlmFlashError(f"{SO_PATH} is missing: build it (python -c 'import __graft_entry__ as g; g.build()')")
+        L = C.CDLL(SO_PATH)
+        for name, (res, args) in SYMBOLS.items():
+            f = getattr(L, name)
+            f.restype, f.argtypes = res, args
+        if L.glmflash_abi_version() != 1 or L.glmflash_config_bytes() != C.sizeof(Config) or \
+                L.glmflash_weights_bytes() != C.sizeof(Weights):
+            raise GlmFlashError("ABI mismatch between the python binding and libglmflash_b200.so")
+        _lib = L
+    return _lib
+
+
+def _check(rc):
+    if rc != 0:
+        raise GlmFlashError(lib().glmflash_error().decode())
+
+
+def make_config(hidden=2048, inter=1536, experts=64, slots=5, max_rows=1, shared_exl3=1, expert_lo=0,
+                expert_hi=None, limit=10.0):
+    return Config(hidden, inter, experts, slots, max_rows, shared_exl3, expert_lo,
+                  experts if expert_hi is None else expert_hi, limit)
+
+
+def _torch():
+    import torch
+    if not torch.cuda.is_available():
+        raise GlmFlashError("no CUDA device: this library has no CPU path")
+    return torch
+
+
+def _stream_ptr(stream=None):
+    torch = _torch()
+    s = stream if stream is not None else torch.cuda.current_stream()
+    return C.c_void_p(s.cuda_stream)
+
+
+def weights_struct(w):
+    """w: mapping name -> CUDA torch tensor (gt/ut/dt int32, scales float16).  Keeps nothing alive."""
+    return Weights(**{n: w[n].data_ptr() for n in WEIGHT_NAMES})
+
+
+def _view(ptr, shape, dtype):
+    """A torch view of library-owned device memory (valid while the owner lives)."""
+    torch = _torch()
+    import numpy as np
+    n = int(np.prod(shape))
+    itemsize = torch.empty((), dtype=dtype).element_size()
+
+    class _Holder:
+        pass
+
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": (n * itemsize,), "typestr": "|u1", "data": (int(ptr), False), "version": 2}
+    return torch.as_tensor(h, device="cuda").view(dtype).view(*shape)
+
+
+def exl3_decode(words, stream=None):
+    """words: int32/uint32-bit CUDA tensor [tiles][32] -> float16 [tiles][16][16] (k, n)."""
+    torch = _torch()
+    tiles = words.numel() // 32
+    out = torch.empty((tiles, 16, 16), dtype=torch.float16, device=words.device)
+    _check(lib().glmflash_exl3_decode(_stream_ptr(stream), words.data_ptr(), tiles, out.data_ptr()))
+    return out
+
+
+def exl3_linear(x, words, suh, svh, K, N, stream=None):
+    """x fp16 [rows][K] (rows <= 16) -> fp16 [rows][N]."""
+    torch = _torch()
+    rows = x.shape[0]
+    nbytes = lib().glmflash_exl3_linear_scratch_bytes(K, N)
+    if nbytes == 0:
+        raise GlmFlashError("unsupported linear shape")
+    scratch = torch.empty(nbytes, dtype=torch.uint8, device=x.device)
+    y = torch.empty((rows, N), dtype=torch.float16, device=x.device)
+    _check(lib().glmflash_exl3_linear(_stream_ptr(stream), x.data_ptr(), rows, words.data_ptr(), suh.data_ptr(),
+                                      svh.data_ptr(), K, N, y.data_ptr(), scratch.data_ptr()))
+    torch.cuda.current_stream().synchronize()      # scratch is freed on return
+    return y
+
+
+class _Owner:
+    _new = _free = None
+
+    def __init__(self, cfg):
+        _torch()
+        self.cfg = cfg
+        self._h = C.c_void_p()
+        _check(getattr(lib(), self._new)(C.byref(cfg), C.sizeof(cfg), C.byref(self._h)))
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            getattr(lib(), self._free)(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class Grouping(_Owner):
+    """Grouping::{new,run} + ids/count/members (reference src/grouping.rs:29-111)."""
+    _new, _free = "glmflash_grouping_new", "glmflash_grouping_free"
+
+    def run(self, picks, rows, stream=None):
+        _check(lib().glmflash_grouping_run(self._h, _stream_ptr(stream), picks.data_ptr(), rows))
+
+    @property
+    def ids(self):
+        import torch
+        return _view(lib().glmflash_grouping_ids(self._h), (self.cfg.experts + 1,), torch.int32)
+
+    @property
+    def count(self):
+        import torch
+        return _view(lib().glmflash_grouping_count(self._h), (1,), torch.int32)
+
+    @property
+    def members(self):
+        import torch
+        return _view(lib().glmflash_grouping_members(self._h), (self.cfg.experts + 1, self.cfg.max_rows), torch.int32)
+
+
+class ExpertGpu(_Owner):
+    """ExpertGpu::{new_rows,run_rows,y} (reference src/experts.rs:382-563)."""
+    _new, _free = "glmflash_experts_new", "glmflash_experts_free"
+
+    def run_rows(self, w, x, picks, ids, count, members, rows, maxm, x_stride=None, stream=None):
+        ws = w if isinstance(w, Weights) else weights_struct(w)
+        _check(lib().glmflash_experts_run_rows(self._h, _stream_ptr(stream), C.byref(ws), x.data_ptr(),
+                                               x_stride or x.stride(0), picks.data_ptr(), ids.data_ptr(),
+                                               count.data_ptr(), members.data_ptr(), rows, maxm))
+
+    @property
+    def y(self):
+        import torch
+        return _view(lib().glmflash_experts_y(self._h), (self.cfg.max_rows * self.cfg.slots, self.cfg.hidden),
+                     torch.float32)
+
+    @property
+    def xd(self):
+        import torch
+        return _view(lib().glmflash_experts_xd(self._h), (self.cfg.max_rows * self.cfg.slots, self.cfg.inter),
+                     torch.float16)
+
+    @property
+    def status(self):
+        import torch
+        return _view(lib().glmflash_experts_status(self._h), (1,), torch.int32)
+
+
+class FastExperts(_Owner):
+    """FastExperts::{new,run,output} (reference src/fast_experts.rs:43-208)."""
+    _new, _free = "glmflash_fast_experts_new", "glmflash_fast_experts_free"
+
+    def run(self, w, x, picks, ids, count, members, rows, maxm, shared_x=False, x_stride=None, stream=None):
+        ws = w if isinstance(w, Weights) else weights_struct(w)
+        _check(lib().glmflash_fast_experts_run(self._h, _stream_ptr(stream), C.byref(ws), x.data_ptr(),
+                                               x_stride or x.stride(0), picks.data_ptr(), ids.data_ptr(),
+                                               count.data_ptr(), members.data_ptr(), rows, maxm, int(shared_x)))
+
+    @property
+    def output(self):
+        import torch
+        return _view(lib().glmflash_fast_experts_output(self._h),
+                     (self.cfg.max_rows * self.cfg.slots, self.cfg.hidden), torch.float32)
+
+    @property
+    def xd(self):
+        import torch
+        return _view(lib().glmflash_fast_experts_xd(self._h), (self.cfg.max_rows * self.cfg.slots, self.cfg.inter),
+                     torch.float16)
+
+
+class Moe(_Owner):
+    """Moe::{new,run,output}: grouping -> experts -> combine (reference src/moe.rs:28-182)."""
+    _new, _free = "glmflash_moe_new", "glmflash_moe_free"
+
+    def run(self, w, x, picks, route_w, rows, x_stride=None, stream=None):
+        ws = w if isinstance(w, Weights) else weights_struct(w)
+        _check(lib().glmflash_moe_run(self._h, _stream_ptr(stream), C.byref(ws), x.data_ptr(),
+                                      x_stride or x.stride(0), picks.data_ptr(), route_w.data_ptr(), rows))
+
+    def run_host(self, w, x_host, picks_host, route_w_host, rows, out_host, stream=None):
+        """Host (pinned) buffers in, host buffer out; synchronises.  The end-to-end entry point."""
+        ws = w if isinstance(w, Weights) else weights_struct(w)
+        _check(lib().glmflash_moe_run_host(self._h, _stream_ptr(stream), C.byref(ws), x_host.data_ptr(),
+                                           self.cfg.hidden, picks_host.data_ptr(), route_w_host.data_ptr(), rows,
+                                           out_host.data_ptr()))
+
+    def set_phases(self, mask):
+        _check(lib().glmflash_moe_set_phases(self._h, mask))
+
+    @property
+    def output(self):
+        import torch
+        return _view(lib().glmflash_moe_output(self._h), (self.cfg.max_rows, self.cfg.hidden), torch.float32)
+
+
+def rank_sum(gathered, out, stream=None):
+    """out[r] = sum over ranks in ascending order of gathered[rank][r] (fp32 [world][rows][H])."""
+    world, rows, H = gathered.shape
+    _check(lib().glmflash_rank_sum(_stream_ptr(stream), gathered.data_ptr(), world, rows, H, out.data_ptr()))
+    return out

@@ -1,0 +1,144 @@
+// Shared device helpers of the B200 EXL3 expert path: the trellis codebook, the 128-point Hadamard
+// transform, rounding helpers, TMA bulk copies with bounded mbarrier waits, and host-side error plumbing.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/glmflash_b200.h"
+
+namespace gf {
+
+constexpr float HAD_SCALE = 0.08838834764831845f;  // 1 / sqrt(128)
+constexpr uint32_t MCG_MUL = 0xCBAC1FEDu;
+constexpr uint32_t MCG_AND = 0x8FFF8FFFu;
+constexpr uint32_t MCG_XOR = 0x3B603B60u;
+
+// ---- host-side error plumbing --------------------------------------------------------------------------
+std::string &last_error();
+int fail(const std::string &msg);
+int fail_cuda(cudaError_t e, const char *what);
+#define GF_CUDA(call)                                             \
+    do {                                                          \
+        cudaError_t gf_e_ = (call);                               \
+        if (gf_e_ != cudaSuccess) return gf::fail_cuda(gf_e_, #call); \
+    } while (0)
+#define GF_REQUIRE(cond, msg)                \
+    do {                                     \
+        if (!(cond)) return gf::fail(msg);   \
+    } while (0)
+
+// ---- codebook ------------------------------------------------------------------------------------------
+// The 32-bit codeword of a 16-bit trellis state: two fp16 halves whose sum is the weight
+// (upstream native/exl3.cu:21-25).
+__device__ __forceinline__ uint32_t codeword(uint32_t state) { return ((state * MCG_MUL) & MCG_AND) ^ MCG_XOR; }
+
+// The weight itself: half-precision sum of the two halves, round to nearest even (upstream :26-29).
+__device__ __forceinline__ __half codebook(uint32_t state) {
+    const uint32_t x = codeword(state);
+    return __hadd(__ushort_as_half((unsigned short)(x & 0xffffu)), __ushort_as_half((unsigned short)(x >> 16)));
+}
+
+// Codewords of the two states packed in u = (state_hi << 16) | state_lo.
+// GF_MCG_MAD = 1 trades two ALU operations (mask, shift) for one multiply-add:
+//   (u & 0xffff) * C  ==  u * C - (((u >> 16) * C) << 16)   (mod 2^32),
+// because the integer-multiply pipe has slack while the ALU pipe is the bottleneck of the GEMV.
+#ifndef GF_MCG_MAD
+#define GF_MCG_MAD 1
+#endif
+__device__ __forceinline__ void codeword_pair(uint32_t u, uint32_t &x_hi, uint32_t &x_lo) {
+    const uint32_t h = u >> 16;
+#if GF_MCG_MAD
+    uint32_t ph, pu, pl;
+    asm("mul.lo.u32 %0, %1, %2;" : "=r"(ph) : "r"(h), "r"(MCG_MUL));
+    asm("mul.lo.u32 %0, %1, %2;" : "=r"(pu) : "r"(u), "r"(MCG_MUL));
+    asm("mad.lo.u32 %0, %1, %2, %3;" : "=r"(pl) : "r"(ph), "r"(0xFFFF0000u), "r"(pu));
+    x_hi = (ph & MCG_AND) ^ MCG_XOR;
+    x_lo = (pl & MCG_AND) ^ MCG_XOR;
+#else
+    x_hi = codeword(h);
+    x_lo = codeword(u & 0xffffu);
+#endif
+}
+
+// ---- rounding helpers (the rounding points of upstream's epilogues, native/exl3.cu:243) ------------------
+__device__ __forceinline__ float bf16r(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
+// ---- Hadamard ------------------------------------------------------------------------------------------
+// 128 values held 4 per lane (lane L: values 4L..4L+3), natural order; butterflies stride 1, 2 in
+// registers, 4..64 across lanes, each (lower + upper, lower - upper): upstream's order
+// (native/exl3.cu:208-219 <=> src/experts.rs:25-42), so sums associate identically.
+__device__ __forceinline__ void fwht128(float (&v)[4], int lane) {
+    const float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+    v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
+#pragma unroll
+    for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float o = __shfl_xor_sync(0xffffffffu, v[j], m);
+            v[j] = (lane & m) ? o - v[j] : v[j] + o;
+        }
+    }
+}
+
+// ---- shared-memory addressing, TMA bulk copy, mbarrier -----------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls and reports false (the caller records an error status and
+// leaves); nothing in this library spins without a bound.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = 4000000u) {
+    for (uint32_t i = 0; i < limit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+// 1-D TMA bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses and the
+// size are multiples of 16 bytes.
+__device__ __forceinline__ void tma_load_1d(void *dst_smem, const void *src_gmem, uint32_t bytes, uint64_t *bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                     smem_u32(dst_smem)),
+                 "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+// Programmatic dependent launch: let the next kernel of the stream start its prologue; wait until the
+// previous kernel's results are visible.  Both are no-ops for a kernel launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Device status word shared by kernels with bounded waits: 0 = fine, otherwise the first failure code.
+enum : int { GF_STATUS_OK = 0, GF_STATUS_TMA_TIMEOUT = 1, GF_STATUS_TMEM = 2, GF_STATUS_MMA_TIMEOUT = 3 };
+
+}  // namespace gf

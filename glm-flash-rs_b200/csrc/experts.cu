@@ -1,0 +1,213 @@
+// ExpertGpu: the decode / verify owner (upstream src/experts.rs:365-563) and the single-linear probe.
+#include <algorithm>
+#include <new>
+
+#include "gemv.cuh"
+
+namespace gf {
+
+template <typename F>
+static int set_smem(F *kernel, size_t bytes) {
+    GF_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+    return 0;
+}
+
+int launch_rot_in(cudaStream_t s, const void *x, bool x_is_bf16, int x_stride, const int *picks, const __half *suh0,
+                  const __half *suh1, __half *out0, __half *out1, int K, int slots, int P, int mats, int E,
+                  int shared_exl3, int e_lo, int e_hi) {
+    const long items = (long)P * (K / 128) * mats;
+    const unsigned grid = (unsigned)((items + 7) / 8);
+    if (x_is_bf16)
+        rot_in_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16 *)x, x_stride, picks, suh0, suh1, out0,
+                                                          out1, K, slots, P, mats, E, shared_exl3, e_lo, e_hi);
+    else
+        rot_in_kernel<__half><<<grid, 256, 0, s>>>((const __half *)x, x_stride, picks, suh0, suh1, out0, out1, K, slots,
+                                                    P, mats, E, shared_exl3, e_lo, e_hi);
+    GF_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax) {
+    const int sets = a.maxm > 8 ? 2 : 1;
+    const size_t smem = gemv_smem_bytes(mats, sets);
+    static bool configured_dev[64] = {};
+    int dev = 0;
+    GF_CUDA(cudaGetDevice(&dev));
+    bool &configured = configured_dev[dev & 63];
+    if (!configured) {
+        if (set_smem(gemv_kernel<2, 1>, gemv_smem_bytes(2, 1))) return -1;
+        if (set_smem(gemv_kernel<2, 2>, gemv_smem_bytes(2, 2))) return -1;
+        if (set_smem(gemv_kernel<1, 1>, gemv_smem_bytes(1, 1))) return -1;
+        if (set_smem(gemv_kernel<1, 2>, gemv_smem_bytes(1, 2))) return -1;
+        configured = true;
+    }
+    const dim3 grid((unsigned)(a.N / 128), (unsigned)a.SK, (unsigned)umax);
+    if (mats == 2 && sets == 1) gemv_kernel<2, 1><<<grid, GEMV_THREADS, smem, s>>>(a);
+    else if (mats == 2) gemv_kernel<2, 2><<<grid, GEMV_THREADS, smem, s>>>(a);
+    else if (sets == 1) gemv_kernel<1, 1><<<grid, GEMV_THREADS, smem, s>>>(a);
+    else gemv_kernel<1, 2><<<grid, GEMV_THREADS, smem, s>>>(a);
+    GF_CUDA(cudaGetLastError());
+    return 0;
+}
+
+int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit) {
+    GF_REQUIRE(cfg != nullptr, "config is null");
+    GF_REQUIRE(cfg_bytes == sizeof(glmflash_config), "config size mismatch (ABI)");
+    GF_REQUIRE(cfg->hidden > 0 && cfg->hidden % 256 == 0, "hidden must be a positive multiple of 256");
+    GF_REQUIRE(cfg->inter > 0 && cfg->inter % 256 == 0, "inter must be a positive multiple of 256");
+    GF_REQUIRE(cfg->experts > 0 && cfg->experts < 1024, "experts must be in 1..1023");
+    GF_REQUIRE(cfg->slots >= 2 && cfg->slots <= 32, "slots must be in 2..32");
+    GF_REQUIRE(cfg->max_rows >= 1 && cfg->max_rows <= max_rows_limit, "max_rows outside the scratch bound");
+    GF_REQUIRE(cfg->expert_lo >= 0 && cfg->expert_hi <= cfg->experts && cfg->expert_lo <= cfg->expert_hi,
+               "expert window must satisfy 0 <= lo <= hi <= experts");
+    GF_REQUIRE(cfg->limit > 0.f, "limit must be positive");
+    int dev_count = 0;
+    if (cudaGetDeviceCount(&dev_count) != cudaSuccess || dev_count == 0) return fail("no CUDA device: there is no CPU path");
+    return 0;
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+struct glmflash_experts {
+    glmflash_config cfg;
+    __half *xg = nullptr, *xu = nullptr, *xd = nullptr;
+    float *z = nullptr, *y = nullptr;
+    int *tickets = nullptr, *status = nullptr;
+    int sk_gu = 0, sk_dn = 0;
+    int phases = 7;                                 // profiling aid: 1 = input rotation, 2 = gate/up, 4 = down
+};
+
+extern "C" int glmflash_experts_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_experts **out) {
+    GF_REQUIRE(out != nullptr, "out is null");
+    *out = nullptr;
+    if (check_config(cfg, cfg_bytes, 16)) return -1;      // upstream: 1..=MAX_ROWS (16), src/experts.rs:391-394
+    glmflash_experts *e = new (std::nothrow) glmflash_experts();
+    GF_REQUIRE(e != nullptr, "out of host memory");
+    e->cfg = *cfg;
+    const size_t H = cfg->hidden, I = cfg->inter, P = (size_t)cfg->max_rows * cfg->slots, E1 = cfg->experts + 1;
+    e->sk_gu = cfg->hidden / GEMV_KC;
+    e->sk_dn = cfg->inter / GEMV_KC;
+    const size_t zf = std::max((size_t)2 * e->sk_gu * P * I, (size_t)e->sk_dn * P * H);
+    const size_t nbmax = std::max(H, I) / 128;
+    auto alloc = [&](void **p, size_t bytes) -> int {
+        GF_CUDA(cudaMalloc(p, bytes));
+        GF_CUDA(cudaMemset(*p, 0, bytes));
+        return 0;
+    };
+    if (alloc((void **)&e->xg, P * H * 2) || alloc((void **)&e->xu, P * H * 2) || alloc((void **)&e->xd, P * I * 2) ||
+        alloc((void **)&e->z, zf * 4) || alloc((void **)&e->y, P * H * 4) ||
+        alloc((void **)&e->tickets, E1 * nbmax * 4) || alloc((void **)&e->status, 4)) {
+        glmflash_experts_free(e);
+        return -1;
+    }
+    *out = e;
+    return 0;
+}
+
+extern "C" void glmflash_experts_free(glmflash_experts *e) {
+    if (!e) return;
+    cudaFree(e->xg); cudaFree(e->xu); cudaFree(e->xd); cudaFree(e->z); cudaFree(e->y);
+    cudaFree(e->tickets); cudaFree(e->status);
+    delete e;
+}
+
+extern "C" int glmflash_experts_run_rows(glmflash_experts *e, void *stream, const glmflash_weights *w, const void *input,
+                                         int x_stride, const int32_t *picks, const int32_t *ids, const int32_t *count,
+                                         const int32_t *members, int rows, int maxm) {
+    GF_REQUIRE(e && w && input && picks && ids && count && members, "null argument");
+    const glmflash_config &c = e->cfg;
+    GF_REQUIRE(rows > 0 && rows <= c.max_rows && maxm >= rows && maxm <= c.max_rows, "expert verifier row/member bounds");
+    GF_REQUIRE(x_stride >= c.hidden && x_stride % 4 == 0, "x_stride must be >= hidden and a multiple of 4");
+    GF_REQUIRE(((uintptr_t)w->gt | (uintptr_t)w->ut | (uintptr_t)w->dt) % 16 == 0, "trellis tensors must be 16-byte aligned");
+    GF_REQUIRE(((uintptr_t)input) % 8 == 0, "input must be 8-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int H = c.hidden, I = c.inter, P = rows * c.slots, E1 = c.experts + 1;
+    const int umax = std::min(rows * (c.slots - 1) + 1, E1);
+    if ((e->phases & 1) &&
+        launch_rot_in(s, input, true, x_stride, picks, (const __half *)w->suh_g, (const __half *)w->suh_u, e->xg, e->xu, H,
+                      c.slots, P, 2, c.experts, c.shared_exl3, c.expert_lo, c.expert_hi))
+        return -1;
+    GemvArgs a{};
+    a.ids = ids; a.count = count; a.members = members;
+    a.Z = e->z; a.tickets = e->tickets; a.status = e->status;
+    a.P = P; a.maxm = maxm; a.slots = c.slots; a.E = c.experts; a.e_lo = c.expert_lo; a.e_hi = c.expert_hi;
+    a.shared_exl3 = c.shared_exl3; a.limit = c.limit;
+    // gate + up, SwiGLU, down-input rotation -> xd
+    a.X0 = e->xg; a.X1 = e->xu; a.T0 = w->gt; a.T1 = w->ut;
+    a.sv0 = (const __half *)w->svh_g; a.sv1 = (const __half *)w->svh_u; a.sd = (const __half *)w->suh_d;
+    a.xd = e->xd; a.y = nullptr; a.K = H; a.N = I; a.SK = e->sk_gu; a.mode = GEMV_GATEUP;
+    if ((e->phases & 2) && launch_gemv(s, 2, a, umax)) return -1;
+    if (!(e->phases & 4)) return 0;
+    // down -> y
+    a.X0 = e->xd; a.X1 = e->xd; a.T0 = w->dt; a.T1 = w->dt;
+    a.sv0 = (const __half *)w->svh_d; a.sv1 = nullptr; a.sd = nullptr;
+    a.xd = nullptr; a.y = e->y; a.K = I; a.N = H; a.SK = e->sk_dn; a.mode = GEMV_DOWN;
+    return launch_gemv(s, 1, a, umax);
+}
+
+extern "C" int glmflash_experts_set_phases(glmflash_experts *e, int mask) {
+    GF_REQUIRE(e != nullptr, "null argument");
+    e->phases = mask;
+    return 0;
+}
+
+extern "C" float *glmflash_experts_y(const glmflash_experts *e) { return e ? e->y : nullptr; }
+extern "C" const uint16_t *glmflash_experts_xd(const glmflash_experts *e) { return e ? (const uint16_t *)e->xd : nullptr; }
+extern "C" const int32_t *glmflash_experts_status(const glmflash_experts *e) { return e ? e->status : nullptr; }
+
+// ---- single EXL3 linear (fp16 in, fp16 out): rot_in + one-matrix GEMV with the fp16 epilogue ---------------
+namespace {
+struct LinearScratch {
+    size_t xr, z, tickets, tables, total;
+};
+LinearScratch linear_layout(int K, int N) {
+    LinearScratch L;
+    size_t off = 0;
+    auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) / 256 * 256; return o; };
+    L.xr = take((size_t)16 * K * 2);
+    L.z = take((size_t)(K / GEMV_KC) * 16 * N * 4);
+    L.tickets = take((size_t)(N / 128) * 4);
+    L.tables = take((size_t)(2 + 16) * 4 + 4);      // ids[1], count[1], members[16], status
+    L.total = off;
+    return L;
+}
+__global__ void linear_tables_kernel(int *tables, int rows) {
+    // ids[0] = 0, count = 1, members[m] = m * 32 (row m, slot 0) for m < rows, else -1; status = 0
+    const int t = threadIdx.x;
+    if (t == 0) { tables[0] = 0; tables[1] = 1; tables[18] = 0; }
+    if (t < 16) tables[2 + t] = t < rows ? t * 32 : -1;
+}
+}  // namespace
+
+extern "C" size_t glmflash_exl3_linear_scratch_bytes(int K, int N) {
+    if (K <= 0 || N <= 0 || K % 256 || N % 128) return 0;
+    return linear_layout(K, N).total;
+}
+
+extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, const uint32_t *words, const uint16_t *suh,
+                                    const uint16_t *svh, int K, int N, uint16_t *y, void *scratch) {
+    GF_REQUIRE(x && words && suh && svh && y && scratch, "null argument");
+    GF_REQUIRE(K > 0 && K % 256 == 0 && N > 0 && N % 128 == 0, "K must be a multiple of 256 and N of 128");
+    GF_REQUIRE(rows >= 1 && rows <= 16, "rows must be in 1..16");
+    GF_REQUIRE(((uintptr_t)words) % 16 == 0 && ((uintptr_t)scratch) % 256 == 0, "words 16-byte, scratch 256-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    const LinearScratch L = linear_layout(K, N);
+    unsigned char *base = (unsigned char *)scratch;
+    int *tables = (int *)(base + L.tables);
+    GF_CUDA(cudaMemsetAsync(base + L.tickets, 0, (size_t)(N / 128) * 4, s));
+    linear_tables_kernel<<<1, 32, 0, s>>>(tables, rows);
+    GF_CUDA(cudaGetLastError());
+    __half *xr = (__half *)(base + L.xr);
+    if (launch_rot_in(s, x, false, K, nullptr, (const __half *)suh, (const __half *)suh, xr, xr, K, 1, rows, 1, 1, 1, 0, 2))
+        return -1;
+    GemvArgs a{};
+    a.X0 = xr; a.X1 = xr; a.T0 = words; a.T1 = words;
+    a.ids = tables; a.count = tables + 1; a.members = tables + 2;
+    a.Z = (float *)(base + L.z); a.tickets = (int *)(base + L.tickets); a.status = tables + 18;
+    a.sv0 = (const __half *)svh; a.xd = (__half *)y;
+    a.K = K; a.N = N; a.P = rows; a.SK = K / GEMV_KC; a.maxm = rows; a.slots = 1; a.E = 1; a.e_lo = 0; a.e_hi = 1;
+    a.shared_exl3 = 1; a.mode = GEMV_LINEAR; a.limit = 10.f;
+    return launch_gemv(s, 1, a, 1);
+}

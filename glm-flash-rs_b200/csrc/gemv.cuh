@@ -1,0 +1,331 @@
+// Grouped EXL3 GEMV for windows of 1..16 rows (decode and speculative verify), sm_100a.
+//
+// Replaces upstream's exl3_grouped_8_4 / exl3_load_nc_8_1 + gateup_epilogue_kernel + down_epilogue_kernel
+// (native/exl3.cu:59-170,260-321, native/expert_loads.cu:130-285).  Same operands and the same member /
+// pair conventions; a different machine mapping:
+//
+//   * work item = (distinct expert u, 128-column block nb, K split): MATS matrices x 16 k-tiles x 8 n-tiles,
+//     i.e. MATS x 16 contiguous 1-KB rows of packed trellis words.  One elected warp issues them all as TMA
+//     bulk copies (cp.async.bulk) into shared memory at kernel start, four k-tiles per mbarrier, so the whole
+//     item is in flight before anything else happens and the copy engine, not the warps, follows the stream.
+//   * a lane reads 16 bytes (4 words of one tile) with one LDS.128: that is 32 weights, all 16 k of two
+//     columns (G, G+8), so only one shuffle per 32 weights is needed for the word that precedes the chunk.
+//     The four lanes of a quad read the same 16-byte slot of four consecutive k-tiles.
+//   * states are cut with funnel shifts in pairs (state_j << 16 | state_{j+4}), multiplied by the codebook
+//     constant, masked, and the two fp16 halves of a codeword are added by one HADD2 whose result carries the
+//     weight in both halves: exactly upstream's fp16 weight (bit-exact decode), without byte permutes.
+//   * the weights are the A operand of mma.m16n8k16 (rows = 16 output columns) over a doubled K: the pair
+//     (w, w) meets (x_k, 0), so a.w is accumulated once, in fp32.  Members (<= 8 per set) are the N dimension;
+//     a second set of B operands serves experts with 9..16 members without decoding twice.
+//   * warps of a CTA own disjoint n-tiles (and matrices / K halves), so nothing is reduced across warps by
+//     atomics; the K splits of an (expert, column block) meet through an fp32 partial buffer Z and the CTA
+//     that arrives last (one atomic ticket per item, reset by the last arriver so graphs replay) sums them in
+//     ascending split order and runs the epilogue: Hadamard, scales, SwiGLU, down-input rotation (MATS = 2)
+//     or Hadamard and output scale (MATS = 1).  No output element depends on arrival order.
+//   * every pair's result depends only on its own row: the split count and tiling are fixed by the shape, and
+//     mma keeps columns (members) independent, so a row of a 16-row window has the bits of the 1-row call.
+#pragma once
+#include "common.cuh"
+
+namespace gf {
+
+constexpr int GEMV_THREADS = 256;
+constexpr int GEMV_KTC = 16;                       // k-tiles per CTA item (per matrix)
+constexpr int GEMV_KC = GEMV_KTC * 16;             // 256 k per CTA item
+constexpr int GEMV_WROW = 1024 + 32;               // bytes per staged weight row (1 KB + 32 B: conflict-free LDS.128)
+constexpr int GEMV_AST = GEMV_KC + 8;              // dwords per staged activation row (+32 B pad)
+constexpr int GEMV_PST = 132;                      // floats per partial row
+
+enum GemvMode : int { GEMV_GATEUP = 0, GEMV_DOWN = 1, GEMV_LINEAR = 2 };
+
+struct GemvArgs {
+    const __half *X0, *X1;        // rotated inputs [P][K] fp16 (X1: second matrix, MATS = 2)
+    const uint32_t *T0, *T1;      // trellis banks [E1][K/16][N/16][32]
+    const int *ids, *count, *members;
+    float *Z;                     // [MATS][SK][P][N] fp32 partials
+    int *tickets;                 // [E1][N/128]
+    const __half *sv0, *sv1, *sd; // gate/up: svh_g, svh_u, suh_d;  down / linear: svh_d
+    __half *xd;                   // gate/up out: [P][N] fp16;  linear out: [P][N] fp16
+    float *y;                     // down out: [P][N] fp32
+    int *status;
+    int K, N, P, SK, maxm, slots, E, e_lo, e_hi, shared_exl3, mode;
+    float limit;
+};
+
+__device__ __forceinline__ bool expert_skipped(int e, int E, int shared_exl3, int e_lo, int e_hi) {
+    // the window [e_lo, e_hi) selects routed experts; the shared expert (id E) is governed by shared_exl3 alone
+    return e < 0 || (e >= E ? !shared_exl3 : (e < e_lo || e >= e_hi));
+}
+
+// (w, w) from a masked codeword: one half-precision add of its two halves.
+__device__ __forceinline__ uint32_t weight_dup(uint32_t x) {
+    const __half2 v = *reinterpret_cast<const __half2 *>(&x);
+    const __half2 r = __hadd2(__low2half2(v), __high2half2(v));
+    return *reinterpret_cast<const uint32_t *>(&r);
+}
+
+// dynamic shared memory size of a launch
+inline size_t gemv_smem_bytes(int mats, int sets) {
+    size_t w = (size_t)mats * GEMV_KTC * GEMV_WROW;
+    size_t part = (size_t)2 * 16 * GEMV_PST * sizeof(float);
+    size_t a = (size_t)mats * sets * 8 * GEMV_AST * 4;
+    return 64 + (w > part ? w : part) + a;
+}
+
+template <int MATS, int SETS>
+__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                         // 4 barriers (one per 4 k-tiles)
+    unsigned char *wsm = smem + 64;                                              // [MATS][16] rows of GEMV_WROW
+    constexpr size_t WBYTES = (size_t)MATS * GEMV_KTC * GEMV_WROW;
+    constexpr size_t PBYTES = (size_t)2 * 16 * GEMV_PST * sizeof(float);
+    constexpr size_t WP = WBYTES > PBYTES ? WBYTES : PBYTES;
+    float *part = reinterpret_cast<float *>(wsm);                                // aliases wsm after the K loop
+    uint32_t *asm_ = reinterpret_cast<uint32_t *>(wsm + WP);                     // [MATS][SETS*8][GEMV_AST]
+    __shared__ int rows_sh[16];
+    __shared__ int last_sh;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = lane >> 2, T = lane & 3;
+    const int nb = blockIdx.x, split = blockIdx.y, u = blockIdx.z;
+    const int KT = a.K >> 4, NTILES = a.N >> 4, NB = a.N >> 7;
+
+    if (tid == 0) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) mbar_init(bars + g, 1);
+        mbar_fence_init();
+    }
+    const int cnt = __ldcg(a.count);
+    const int e = __ldcg(a.ids + u);
+    if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the CTA
+    __syncthreads();
+
+    // ---- the whole item's packed words, in flight at once
+    const int kt0 = split * GEMV_KTC;
+    if (warp == 0) {
+        if (lane == 0) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) mbar_expect_tx(bars + g, MATS * 4 * 1024);
+        }
+        __syncwarp();
+        for (int r = lane; r < MATS * GEMV_KTC; r += 32) {
+            const int mat = r / GEMV_KTC, ktl = r % GEMV_KTC;
+            const uint32_t *T_ = mat ? a.T1 : a.T0;
+            const uint32_t *src = T_ + (((size_t)e * KT + kt0 + ktl) * NTILES + (size_t)nb * 8) * 32;
+            tma_load_1d(wsm + (size_t)r * GEMV_WROW, src, 1024, bars + (ktl >> 2));
+        }
+    }
+    pdl_launch_dependents();
+
+    // ---- members of this expert: pair rows
+    if (tid < 16) {
+        const int code = tid < a.maxm ? __ldcg(a.members + (size_t)u * a.maxm + tid) : -1;
+        rows_sh[tid] = code >= 0 ? (code >> 5) * a.slots + (code & 31) : -1;
+    }
+    pdl_wait();                                   // X / Z / tickets belong to the kernels before this one
+    __syncthreads();
+    int nmem = 0;
+#pragma unroll
+    for (int m = 0; m < 16; ++m) nmem += rows_sh[m] >= 0;   // members come first
+
+    // ---- stage the members' activations of this K range as (x_k, 0) pairs, permuted to the mma order:
+    //      dword position of local k = 64 g + 16 T + 8 h + 2 t + b  is  g*64 + (2t + h)*8 + 2T + b
+    {
+        const int k0 = kt0 * 16;
+        for (int i = tid; i < MATS * SETS * 8 * (GEMV_KC / 2); i += GEMV_THREADS) {
+            const int kp = i % (GEMV_KC / 2), m = (i / (GEMV_KC / 2)) % (SETS * 8), mat = i / ((GEMV_KC / 2) * SETS * 8);
+            const int p = rows_sh[m];
+            uint32_t v = 0u;
+            if (p >= 0) v = __ldcg(reinterpret_cast<const uint32_t *>((mat ? a.X1 : a.X0) + (size_t)p * a.K + k0) + kp);
+            const int kl = 2 * kp;
+            const int g = kl >> 6, TT = (kl >> 4) & 3, h = (kl >> 3) & 1, t = (kl >> 1) & 3;
+            const int pos = g * 64 + (2 * t + h) * 8 + 2 * TT;
+            *reinterpret_cast<uint2 *>(asm_ + ((size_t)mat * SETS * 8 + m) * GEMV_AST + pos) =
+                make_uint2(v & 0xffffu, v >> 16);
+        }
+    }
+    __syncthreads();
+
+    // ---- K loop.  MATS = 2: warp = (matrix, n-tile pair), all 4 groups.  MATS = 1: warp = (K half, pair).
+    const int sub = warp >> 2, ntp = warp & 3;
+    const int mat = MATS == 2 ? sub : 0;
+    const int g_begin = MATS == 2 ? 0 : sub * 2, g_end = MATS == 2 ? 4 : sub * 2 + 2;
+    const bool two_sets = SETS == 2 && nmem > 8;
+    float acc[2][SETS][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int s = 0; s < SETS; ++s)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[n][s][c] = 0.f;
+
+    bool ok = true;
+    for (int g = g_begin; g < g_end; ++g) {
+        if (!mbar_wait(bars + g, 0)) { ok = false; break; }
+        // B operands of the group's 8 mma: (x, 0) pairs of member G (set 0) and member 8 + G (set 1)
+        uint2 b[SETS][8];
+#pragma unroll
+        for (int s = 0; s < SETS; ++s) {
+            const uint32_t *ar = asm_ + ((size_t)mat * SETS * 8 + s * 8 + G) * GEMV_AST + g * 64 + 2 * T;
+#pragma unroll
+            for (int m = 0; m < 8; ++m) b[s][m] = *reinterpret_cast<const uint2 *>(ar + m * 8);
+        }
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+            const uint4 wv = *reinterpret_cast<const uint4 *>(wsm + ((size_t)mat * GEMV_KTC + 4 * g + T) * GEMV_WROW +
+                                                               (ntp * 2 + n) * 128 + G * 16);
+            const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+            const uint32_t before = __shfl_sync(0xffffffffu, wv.w, (lane + 28) & 31);   // word 4G-1 (circular)
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const uint32_t pw = t == 0 ? before : w[t - 1];
+                uint32_t uu[4];
+                uu[0] = __funnelshift_r(w[t], pw, 12);
+                uu[1] = __funnelshift_r(w[t], pw, 8);
+                uu[2] = __funnelshift_r(w[t], pw, 4);
+                uu[3] = w[t];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t x0, x1, x2, x3, af[4];
+                    codeword_pair(uu[2 * h], x0, x1);        // k = 2t + 8h:     columns G, G + 8
+                    codeword_pair(uu[2 * h + 1], x2, x3);    // k = 2t + 8h + 1: columns G, G + 8
+                    af[0] = weight_dup(x0); af[1] = weight_dup(x1); af[2] = weight_dup(x2); af[3] = weight_dup(x3);
+                    const int m = 2 * t + h;
+                    mma16816(acc[n][0], af, b[0][m].x, b[0][m].y);
+                    if (SETS == 2 && two_sets) mma16816(acc[n][SETS - 1], af, b[SETS - 1][m].x, b[SETS - 1][m].y);
+                }
+            }
+        }
+    }
+    if (!ok && lane == 0) atomicExch(a.status, GF_STATUS_TMA_TIMEOUT);
+    __syncthreads();                                // wsm is dead: part aliases it
+
+    // ---- partial[sub][member][column]
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int s = 0; s < SETS; ++s) {
+            const int col = (ntp * 2 + n) * 16 + G, mem = s * 8 + 2 * T;
+            float *pp = part + ((size_t)sub * 16 + mem) * GEMV_PST + col;
+            pp[0] = acc[n][s][0];
+            pp[GEMV_PST] = acc[n][s][1];
+            pp[8] = acc[n][s][2];
+            pp[GEMV_PST + 8] = acc[n][s][3];
+        }
+    __syncthreads();
+    for (int i = tid; i < MATS * 16 * 32; i += GEMV_THREADS) {
+        const int c4 = i & 31, m = (i >> 5) & 15, mt = i >> 9;
+        if (m >= nmem || (SETS == 1 && m >= 8)) continue;
+        float4 v = *reinterpret_cast<const float4 *>(part + ((size_t)mt * 16 + m) * GEMV_PST + 4 * c4);
+        if (MATS == 1) {
+            const float4 w2 = *reinterpret_cast<const float4 *>(part + ((size_t)16 + m) * GEMV_PST + 4 * c4);
+            v.x += w2.x; v.y += w2.y; v.z += w2.z; v.w += w2.w;
+        }
+        float *z = a.Z + (((size_t)mt * a.SK + split) * a.P + rows_sh[m]) * a.N + nb * 128 + 4 * c4;
+        __stcg(reinterpret_cast<float4 *>(z), v);
+    }
+
+    // ---- the last split to arrive sums the partials in split order and finishes the block
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        int *ticket = a.tickets + (size_t)u * NB + nb;
+        const int prev = atomicAdd(ticket, 1);
+        const int last = prev == a.SK - 1;
+        if (last) *ticket = 0;                    // ready for the next launch or graph replay
+        last_sh = last;
+    }
+    __syncthreads();
+    if (!last_sh) return;
+    __threadfence();
+
+    for (int m = warp; m < nmem; m += GEMV_THREADS / 32) {
+        const int p = rows_sh[m];
+        const int n0 = nb * 128 + 4 * lane;
+        float v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int s = 0; s < a.SK; ++s) {
+            const float4 q = __ldcg(reinterpret_cast<const float4 *>(a.Z + (((size_t)s) * a.P + p) * a.N + n0));
+            v0[0] += q.x; v0[1] += q.y; v0[2] += q.z; v0[3] += q.w;
+            if (MATS == 2) {
+                const float4 r = __ldcg(reinterpret_cast<const float4 *>(a.Z + (((size_t)a.SK + s) * a.P + p) * a.N + n0));
+                v1[0] += r.x; v1[1] += r.y; v1[2] += r.z; v1[3] += r.w;
+            }
+        }
+        fwht128(v0, lane);
+        if (MATS == 2) {
+            fwht128(v1, lane);
+            const __half *sg = a.sv0 + (size_t)e * a.N + n0, *su = a.sv1 + (size_t)e * a.N + n0,
+                         *sd = a.sd + (size_t)e * a.N + n0;
+            float o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float gg = fminf(bf16r(v0[j] * HAD_SCALE * __half2float(sg[j])), a.limit);
+                const float uu = fminf(fmaxf(bf16r(v1[j] * HAD_SCALE * __half2float(su[j])), -a.limit), a.limit);
+                const float act = bf16r(bf16r(gg / (1.f + expf(-gg))) * uu);
+                o[j] = act * __half2float(sd[j]);
+            }
+            fwht128(o, lane);
+            __half2 h01 = __halves2half2(__float2half_rn(o[0] * HAD_SCALE), __float2half_rn(o[1] * HAD_SCALE));
+            __half2 h23 = __halves2half2(__float2half_rn(o[2] * HAD_SCALE), __float2half_rn(o[3] * HAD_SCALE));
+            uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+            *reinterpret_cast<uint2 *>(a.xd + (size_t)p * a.N + n0) = pk;
+        } else {
+            const __half *sv = a.sv0 + (size_t)e * a.N + n0;
+            float4 o;
+            o.x = v0[0] * HAD_SCALE * __half2float(sv[0]);
+            o.y = v0[1] * HAD_SCALE * __half2float(sv[1]);
+            o.z = v0[2] * HAD_SCALE * __half2float(sv[2]);
+            o.w = v0[3] * HAD_SCALE * __half2float(sv[3]);
+            if (a.mode == GEMV_LINEAR) {
+                __half2 h01 = __halves2half2(__float2half_rn(o.x), __float2half_rn(o.y));
+                __half2 h23 = __halves2half2(__float2half_rn(o.z), __float2half_rn(o.w));
+                uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+                *reinterpret_cast<uint2 *>(a.xd + (size_t)p * a.N + n0) = pk;
+            } else {
+                *reinterpret_cast<float4 *>(a.y + (size_t)p * a.N + n0) = o;
+            }
+        }
+    }
+}
+
+// Input rotation (upstream rot_in_kernel, native/exl3.cu:224-241): one warp per (pair, 128-block, matrix);
+// out[mat][p][blk] = fp16(H(x[row] * suh[mat][e]) / sqrt(128)).  IN = __nv_bfloat16 (layer input) or __half.
+// picks == nullptr: pair p is row p of expert 0 (the single-linear probe).
+template <typename IN>
+__global__ void __launch_bounds__(256) rot_in_kernel(const IN *__restrict__ x, int x_stride, const int *__restrict__ picks,
+                                                     const __half *__restrict__ suh0, const __half *__restrict__ suh1,
+                                                     __half *__restrict__ out0, __half *__restrict__ out1, int K, int slots,
+                                                     int P, int mats, int E, int shared_exl3, int e_lo, int e_hi) {
+    pdl_launch_dependents();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = K >> 7;
+    const long item = (long)blockIdx.x * 8 + warp;
+    if (item >= (long)P * KB * mats) return;
+    const int blk = (int)(item % KB);
+    const int p = (int)((item / KB) % P), mat = (int)(item / ((long)KB * P));
+    int row = p, e = 0;
+    if (picks) {
+        row = p / slots;
+        e = picks[p];
+        if (expert_skipped(e, E, shared_exl3, e_lo, e_hi)) return;
+    }
+    pdl_wait();
+    const __half *suh = (mat ? suh1 : suh0) + (size_t)e * K + blk * 128 + 4 * lane;
+    const IN *xr = x + (size_t)row * x_stride + blk * 128 + 4 * lane;
+    float v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = (float)xr[j] * __half2float(suh[j]);
+    fwht128(v, lane);
+    __half *o = (mat ? out1 : out0) + (size_t)p * K + blk * 128 + 4 * lane;
+    __half2 h01 = __halves2half2(__float2half_rn(v[0] * HAD_SCALE), __float2half_rn(v[1] * HAD_SCALE));
+    __half2 h23 = __halves2half2(__float2half_rn(v[2] * HAD_SCALE), __float2half_rn(v[3] * HAD_SCALE));
+    *reinterpret_cast<uint2 *>(o) = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+}
+
+// Host-side launch helpers (defined in experts.cu).
+int launch_rot_in(cudaStream_t s, const void *x, bool x_is_bf16, int x_stride, const int *picks, const __half *suh0,
+                  const __half *suh1, __half *out0, __half *out1, int K, int slots, int P, int mats, int E,
+                  int shared_exl3, int e_lo, int e_hi);
+int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax);
+
+}  // namespace gf

@@ -1,0 +1,160 @@
+// Moe: grouping -> experts -> combine for one window (upstream src/moe.rs:11-182 for one row,
+// src/model_verifier.rs:1291-1305 and src/batch.rs:1160-1210 for windows and chunks), plus the rank-ordered
+// sum that follows the cross-GPU all-gather (upstream src/model.rs:485-496).
+#include <algorithm>
+#include <new>
+
+#include "common.cuh"
+
+namespace gf {
+int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
+
+// out[r][d] = sum_{s < slots-1, expert computed here} w[r][s] * Y[r*slots+s][d]  (+ Y[shared pair] if computed here)
+// fp32, ascending slot order, shared last: the order of the oracle's combine.
+__global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
+                                                      const float *__restrict__ route_w, float *__restrict__ out, int rows,
+                                                      int slots, int H, int E, int shared_exl3, int e_lo, int e_hi) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int r = blockIdx.y;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (d >= H) return;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < slots; ++s) {
+        const int e = picks[r * slots + s];
+        const bool skip = e < 0 || (e >= E ? !shared_exl3 : (e < e_lo || e >= e_hi));
+        if (skip) continue;
+        const float w = s == slots - 1 ? 1.f : route_w[r * slots + s];
+        const float4 y = *reinterpret_cast<const float4 *>(Y + ((size_t)r * slots + s) * H + d);
+        if (s == slots - 1) { acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w; }
+        else { acc.x += w * y.x; acc.y += w * y.y; acc.z += w * y.z; acc.w += w * y.w; }
+    }
+    *reinterpret_cast<float4 *>(out + (size_t)r * H + d) = acc;
+}
+
+__global__ void __launch_bounds__(256) rank_sum_kernel(const float *__restrict__ gathered, int world, size_t n,
+                                                       float *__restrict__ out) {
+    const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    float4 acc = *reinterpret_cast<const float4 *>(gathered + i);
+    for (int k = 1; k < world; ++k) {
+        const float4 v = *reinterpret_cast<const float4 *>(gathered + (size_t)k * n + i);
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4 *>(out + i) = acc;
+}
+
+int launch_combine(cudaStream_t s, const float *Y, const int *picks, const float *route_w, float *out, int rows,
+                   const glmflash_config &c) {
+    const dim3 grid((unsigned)((c.hidden / 4 + 255) / 256), (unsigned)rows);
+    combine_kernel<<<grid, 256, 0, s>>>(Y, picks, route_w, out, rows, c.slots, c.hidden, c.experts, c.shared_exl3,
+                                        c.expert_lo, c.expert_hi);
+    GF_CUDA(cudaGetLastError());
+    return 0;
+}
+}  // namespace gf
+
+using namespace gf;
+
+struct glmflash_moe {
+    glmflash_config cfg;
+    glmflash_grouping *grouping = nullptr;
+    glmflash_experts *experts = nullptr;            // windows of <= 16 rows
+    glmflash_fast_experts *fast = nullptr;          // chunks of > 16 rows
+    float *out = nullptr;
+    void *in_dev = nullptr;                         // staging for run_host
+    int *picks_dev = nullptr;
+    float *w_dev = nullptr;
+    int phases = 31;                                // profiling aid, see glmflash_moe_set_phases
+};
+
+extern "C" int glmflash_moe_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_moe **out) {
+    GF_REQUIRE(out != nullptr, "out is null");
+    *out = nullptr;
+    if (check_config(cfg, cfg_bytes, 8192)) return -1;
+    glmflash_moe *m = new (std::nothrow) glmflash_moe();
+    GF_REQUIRE(m != nullptr, "out of host memory");
+    m->cfg = *cfg;
+    int rc = glmflash_grouping_new(cfg, cfg_bytes, &m->grouping);
+    if (!rc) rc = cfg->max_rows <= 16 ? glmflash_experts_new(cfg, cfg_bytes, &m->experts)
+                                      : glmflash_fast_experts_new(cfg, cfg_bytes, &m->fast);
+    const size_t rows = cfg->max_rows;
+    if (!rc && cudaMalloc((void **)&m->out, rows * cfg->hidden * 4) != cudaSuccess) rc = fail("cudaMalloc(moe out)");
+    if (!rc && cudaMalloc(&m->in_dev, rows * cfg->hidden * 2) != cudaSuccess) rc = fail("cudaMalloc(moe staging)");
+    if (!rc && cudaMalloc((void **)&m->picks_dev, rows * cfg->slots * 4) != cudaSuccess) rc = fail("cudaMalloc(moe staging)");
+    if (!rc && cudaMalloc((void **)&m->w_dev, rows * cfg->slots * 4) != cudaSuccess) rc = fail("cudaMalloc(moe staging)");
+    if (rc) {
+        glmflash_moe_free(m);
+        return -1;
+    }
+    cudaMemset(m->out, 0, rows * cfg->hidden * 4);
+    *out = m;
+    return 0;
+}
+
+extern "C" void glmflash_moe_free(glmflash_moe *m) {
+    if (!m) return;
+    glmflash_grouping_free(m->grouping);
+    glmflash_experts_free(m->experts);
+    glmflash_fast_experts_free(m->fast);
+    cudaFree(m->out); cudaFree(m->in_dev); cudaFree(m->picks_dev); cudaFree(m->w_dev);
+    delete m;
+}
+
+extern "C" int glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_weights *w, const void *input, int x_stride,
+                                const int32_t *picks, const float *route_w, int rows) {
+    GF_REQUIRE(m && w && input && picks && route_w, "null argument");
+    GF_REQUIRE(rows > 0 && rows <= m->cfg.max_rows, "rows outside the scratch bound");
+    if ((m->phases & 1) && glmflash_grouping_run(m->grouping, stream, picks, rows)) return -1;
+    const int32_t *ids = glmflash_grouping_ids(m->grouping), *count = glmflash_grouping_count(m->grouping),
+                  *members = glmflash_grouping_members(m->grouping);
+    const float *Y;
+    if (m->experts) {
+        if (glmflash_experts_run_rows(m->experts, stream, w, input, x_stride, picks, ids, count, members, rows,
+                                      m->cfg.max_rows))
+            return -1;
+        Y = glmflash_experts_y(m->experts);
+    } else {
+        if (glmflash_fast_experts_run(m->fast, stream, w, input, x_stride, picks, ids, count, members, rows,
+                                      m->cfg.max_rows, w->suh_g == w->suh_u))
+            return -1;
+        Y = glmflash_fast_experts_output(m->fast);
+    }
+    if (!(m->phases & 16)) return 0;
+    return launch_combine((cudaStream_t)stream, Y, picks, route_w, m->out, rows, m->cfg);
+}
+
+extern "C" int glmflash_moe_set_phases(glmflash_moe *m, int mask) {
+    GF_REQUIRE(m != nullptr, "null argument");
+    GF_REQUIRE(m->experts != nullptr, "phase selection exists for the decode / verify pipeline only");
+    m->phases = mask;
+    return glmflash_experts_set_phases(m->experts, (mask >> 1) & 7);
+}
+
+extern "C" float *glmflash_moe_output(const glmflash_moe *m) { return m ? m->out : nullptr; }
+
+extern "C" int glmflash_moe_run_host(glmflash_moe *m, void *stream, const glmflash_weights *w, const void *input_host,
+                                     int x_stride, const int32_t *picks_host, const float *route_w_host, int rows,
+                                     float *out_host) {
+    GF_REQUIRE(m && w && input_host && picks_host && route_w_host && out_host, "null argument");
+    GF_REQUIRE(rows > 0 && rows <= m->cfg.max_rows, "rows outside the scratch bound");
+    GF_REQUIRE(x_stride == m->cfg.hidden, "run_host takes densely packed rows (x_stride == hidden)");
+    cudaStream_t s = (cudaStream_t)stream;
+    const size_t H = m->cfg.hidden, S = m->cfg.slots;
+    GF_CUDA(cudaMemcpyAsync(m->in_dev, input_host, (size_t)rows * H * 2, cudaMemcpyHostToDevice, s));
+    GF_CUDA(cudaMemcpyAsync(m->picks_dev, picks_host, (size_t)rows * S * 4, cudaMemcpyHostToDevice, s));
+    GF_CUDA(cudaMemcpyAsync(m->w_dev, route_w_host, (size_t)rows * S * 4, cudaMemcpyHostToDevice, s));
+    if (glmflash_moe_run(m, stream, w, m->in_dev, x_stride, m->picks_dev, m->w_dev, rows)) return -1;
+    GF_CUDA(cudaMemcpyAsync(out_host, m->out, (size_t)rows * H * 4, cudaMemcpyDeviceToHost, s));
+    GF_CUDA(cudaStreamSynchronize(s));
+    return 0;
+}
+
+extern "C" int glmflash_rank_sum(void *stream, const float *gathered, int world, int rows, int hidden, float *out) {
+    GF_REQUIRE(gathered && out, "null argument");
+    GF_REQUIRE(world >= 1 && rows >= 1 && hidden >= 4 && hidden % 4 == 0, "bad shape");
+    const size_t n = (size_t)rows * hidden;
+    rank_sum_kernel<<<(unsigned)((n / 4 + 255) / 256), 256, 0, (cudaStream_t)stream>>>(gathered, world, n, out);
+    GF_CUDA(cudaGetLastError());
+    return 0;
+}

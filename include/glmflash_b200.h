@@ -1,0 +1,159 @@
+/*
+ * glmflash_b200 -- C ABI of the B200 (sm_100a) EXL3 MoE expert path.
+ *
+ * The library is a drop-in for the routed-expert hot path of cuylerstuwe/glm-flash-rs.  Upstream, Rust
+ * owners (`ExpertGpu`, `FastExperts`, `Grouping`, `Moe`) allocate scratch through the CUDA driver and
+ * launch precompiled kernels by symbol (src/cuda.rs:657-757).  Here each owner is an opaque handle
+ * behind plain-C entry points; a Rust (or any other) host binds them with `extern "C"` exactly as
+ * upstream binds its other native libraries (native/roce_bridge.cpp:22-104, src/roce.rs:89-141).
+ *
+ * Conventions (the same as upstream's native bridges):
+ *   - every call returns 0 on success and -1 on failure; the message of the last failure on the calling
+ *     thread is glmflash_error();  no exception, trap or exit crosses the boundary;
+ *   - handles are single-owner: no concurrent calls on one handle;
+ *   - run functions only enqueue work on the caller's stream: they never synchronise, allocate or read
+ *     back, and may be captured into a CUDA graph and replayed (src/experts.rs:309-316,
+ *     src/fast_experts.rs:383-412);
+ *   - the handle owns scratch and outputs (zero-initialised at construction, src/experts.rs:395-429); the
+ *     caller owns weights, inputs, routing tables and the stream; outputs stay valid until the next run on
+ *     the handle;
+ *   - all pointers are device pointers unless a name ends in `_host`;
+ *   - there is no CPU fallback: without a CUDA device every constructor fails.
+ *
+ * Tensor layouts (src/experts.rs:146-156 with the model sizes as parameters):
+ *   gt, ut  uint32 [E1][H/16][I/16][32]   trellis tiles of the gate / up projections (H -> I)
+ *   dt      uint32 [E1][I/16][H/16][32]   trellis tiles of the down projection (I -> H)
+ *   suh_g, suh_u fp16 [E1][H];  suh_d fp16 [E1][I]     input sign/scale vectors
+ *   svh_g, svh_u fp16 [E1][I];  svh_d fp16 [E1][H]     output sign/scale vectors
+ * E1 = experts + 1: the shared expert is expert id `experts` (the last bank entry).
+ *   picks   int32 [rows][slots]: slots-1 distinct routed ids, then the shared id `experts`
+ *   ids     int32 [E1], count int32 [1], members int32 [E1][maxm]   (the grouping, native/grouping.cu)
+ *           member code = row * 32 + slot, ascending rows first, -1 padded
+ *   pair index p = row * slots + slot  (native/exl3.cu:160-166,228-231)
+ */
+#ifndef GLMFLASH_B200_H
+#define GLMFLASH_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GLMFLASH_ABI_VERSION 1
+
+/* Model sizes and policy of one expert bank.  Passed by pointer with its size (glmflash_config_bytes)
+ * so that host and library can detect a layout mismatch (native/roce_bridge.cpp:29, src/roce.rs:137-141). */
+typedef struct glmflash_config {
+    int32_t hidden;        /* H: model width, multiple of 256 (upstream 4096; benchmark 2048)             */
+    int32_t inter;         /* I: expert intermediate width, multiple of 256 (upstream 512/rank; 1536)      */
+    int32_t experts;       /* E: routed experts; the shared expert has id E                                */
+    int32_t slots;         /* S: top-k + 1 (upstream 9; benchmark 5), at most 32                            */
+    int32_t max_rows;      /* scratch capacity in rows                                                     */
+    int32_t shared_exl3;   /* 1: the shared expert (id E) is an EXL3 expert of the bank and is computed here;
+                              0: upstream behaviour, ids >= E are skipped (native/exl3.cu:151)             */
+    int32_t expert_lo;     /* expert-parallel window: of the routed experts only ids in [expert_lo,        */
+    int32_t expert_hi;     /* expert_hi) are computed here (0, E = all of them)                            */
+    float   limit;         /* SwiGLU clamp (upstream 10.0, src/experts.rs:521)                             */
+    int32_t reserved[7];
+} glmflash_config;
+
+/* The nine tensors `m.pointer(..moe.experts.*)` resolves upstream (src/experts.rs:467). */
+typedef struct glmflash_weights {
+    const uint32_t *gt, *ut, *dt;
+    const uint16_t *suh_g, *suh_u, *suh_d;
+    const uint16_t *svh_g, *svh_u, *svh_d;
+} glmflash_weights;
+
+int         glmflash_abi_version(void);
+size_t      glmflash_config_bytes(void);
+size_t      glmflash_weights_bytes(void);
+const char *glmflash_error(void);                 /* last error of this thread ("" if none) */
+
+/* ---- trellis decode and a single EXL3 linear (building blocks; parity probes) --------------------- */
+
+/* Decode `tiles` 16x16 tiles: words [tiles][32] -> out fp16 [tiles][16][16] (row k, column n), bit-exact
+ * with upstream's decode (native/exl3.cu:21-40 <=> src/experts.rs:43-74). */
+int glmflash_exl3_decode(void *stream, const uint32_t *words, int64_t tiles, uint16_t *out);
+
+/* y[rows][N] fp16 = H(fp16(H(x*suh)/sqrt128) @ W_q)/sqrt128 * svh for fp16 x[rows][K], rows <= 16
+ * (one matrix of src/experts.rs:100-135).  scratch: at least glmflash_exl3_linear_scratch_bytes(K,N). */
+size_t glmflash_exl3_linear_scratch_bytes(int K, int N);
+int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, const uint32_t *words, const uint16_t *suh,
+                         const uint16_t *svh, int K, int N, uint16_t *y, void *scratch);
+
+/* ---- Grouping  (src/grouping.rs:29-111; kernels native/grouping.cu) --------------------------------- */
+typedef struct glmflash_grouping glmflash_grouping;
+int  glmflash_grouping_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_grouping **out);
+void glmflash_grouping_free(glmflash_grouping *g);
+/* Grouping::run(s, picks, rows): fills ids / count / members ([E1][max_rows]).  1 <= rows <= max_rows. */
+int  glmflash_grouping_run(glmflash_grouping *g, void *stream, const int32_t *picks, int rows);
+const int32_t *glmflash_grouping_ids(const glmflash_grouping *g);
+const int32_t *glmflash_grouping_count(const glmflash_grouping *g);
+const int32_t *glmflash_grouping_members(const glmflash_grouping *g);
+
+/* ---- ExpertGpu: decode / verify windows of 1..16 rows  (src/experts.rs:365-563) --------------------- */
+typedef struct glmflash_experts glmflash_experts;
+/* ExpertGpu::new_rows(d, native, max_rows); max_rows in 1..16 (src/experts.rs:391-394). */
+int  glmflash_experts_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_experts **out);
+void glmflash_experts_free(glmflash_experts *e);
+/* ExpertGpu::run_rows(stream, .., input, picks, ids, count, members, rows, maxm).  input: bf16
+ * [rows][x_stride].  Bounds as upstream: 1 <= rows <= max_rows, rows <= maxm <= max_rows
+ * (src/experts.rs:461-464).  Result: glmflash_experts_y() = Y fp32 [rows*slots][H]; rows of pairs whose
+ * expert is skipped (shared_exl3 = 0, or outside the expert window) are left untouched. */
+int  glmflash_experts_run_rows(glmflash_experts *e, void *stream, const glmflash_weights *w, const void *input,
+                               int x_stride, const int32_t *picks, const int32_t *ids, const int32_t *count,
+                               const int32_t *members, int rows, int maxm);
+float *glmflash_experts_y(const glmflash_experts *e);
+/* Down-projection inputs Xd fp16 [rows*slots][I] of the last run (upstream's `xd`; probes compare it). */
+const uint16_t *glmflash_experts_xd(const glmflash_experts *e);
+/* Device status word (int32): 0 after a clean run; non-zero when a bounded wait inside a kernel gave up
+ * (the analogue of upstream's poison word, native/roce.cu:127-141).  Read it after synchronising. */
+const int32_t *glmflash_experts_status(const glmflash_experts *e);
+/* Profiling aid in the spirit of upstream's PROBE modes (native/expert_loads.cu:46-47): run only the selected
+ * kernels of the pipeline (1 = input rotation, 2 = gate/up GEMV + SwiGLU epilogue, 4 = down GEMV + epilogue;
+ * default 7).  Skipped phases leave the scratch of the previous run in place; results are then meaningless. */
+int  glmflash_experts_set_phases(glmflash_experts *e, int mask);
+
+/* ---- FastExperts: prefill chunks of up to 8192 rows  (src/fast_experts.rs:27-208) ------------------- */
+typedef struct glmflash_fast_experts glmflash_fast_experts;
+int  glmflash_fast_experts_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_fast_experts **out);
+void glmflash_fast_experts_free(glmflash_fast_experts *f);
+/* FastExperts::run(s, .., input, picks, ids, count, members, rows, maxm, shared_x).  shared_x != 0 when
+ * suh_g == suh_u so one rotated copy of the input serves both projections (src/batch.rs:195-201). */
+int  glmflash_fast_experts_run(glmflash_fast_experts *f, void *stream, const glmflash_weights *w,
+                               const void *input, int x_stride, const int32_t *picks, const int32_t *ids,
+                               const int32_t *count, const int32_t *members, int rows, int maxm, int shared_x);
+float *glmflash_fast_experts_output(const glmflash_fast_experts *f);       /* fp32 [rows*slots][H] */
+const uint16_t *glmflash_fast_experts_xd(const glmflash_fast_experts *f);  /* fp16 [rows*slots][I] */
+
+/* ---- Moe: the whole layer after routing  (src/moe.rs:11-182, src/batch.rs:1160-1210) ---------------- */
+typedef struct glmflash_moe glmflash_moe;
+/* max_rows <= 16 builds the decode / verify pipeline, larger the prefill pipeline. */
+int  glmflash_moe_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_moe **out);
+void glmflash_moe_free(glmflash_moe *m);
+/* group -> routed and shared experts -> combine:
+ *   out[r][:] = sum_{s < slots-1} route_w[r][s] * Y[r][s][:] + Y[r][slots-1][:]     (fp32 [rows][H])
+ * With an expert window the sum covers this GPU's experts only (a partial for the cross-GPU sum).
+ * route_w: fp32 [rows][slots] (the last entry of a row is not read). */
+int  glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_weights *w, const void *input, int x_stride,
+                      const int32_t *picks, const float *route_w, int rows);
+float *glmflash_moe_output(const glmflash_moe *m);
+/* Profiling aid: 1 = grouping, 2 / 4 / 8 = the three ExpertGpu phases above, 16 = combine (default 31). */
+int  glmflash_moe_set_phases(glmflash_moe *m, int mask);
+/* Host-buffer convenience used by the end-to-end measurement: copies input / picks / route_w from host
+ * memory, runs, copies out[rows][H] back, and synchronises the stream. */
+int  glmflash_moe_run_host(glmflash_moe *m, void *stream, const glmflash_weights *w, const void *input_host,
+                           int x_stride, const int32_t *picks_host, const float *route_w_host, int rows,
+                           float *out_host);
+
+/* ---- expert-parallel combine over NVLink ------------------------------------------------------------ */
+/* out[r][:] = sum over ranks (ascending rank order) of gathered[rank][r][:], the fixed-order sum upstream
+ * applies after its all-gather (src/model.rs:485-496, src/comm.rs:1-2).  gathered: fp32 [world][rows][H]. */
+int glmflash_rank_sum(void *stream, const float *gathered, int world, int rows, int hidden, float *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GLMFLASH_B200_H */
