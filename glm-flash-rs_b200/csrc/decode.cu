@@ -24,9 +24,9 @@ __global__ void __launch_bounds__(256) decode_tiles_kernel(const uint32_t *__res
 }  // namespace gf
 
 extern "C" int glmflash_exl3_decode(void *stream, const uint32_t *words, int64_t tiles, uint16_t *out) {
-    GF_REQUIRE(words && out, "null argument");
     GF_REQUIRE(tiles >= 0 && tiles < ((int64_t)1 << 34), "tile count out of range");
-    if (tiles == 0) return 0;
+    if (tiles == 0) return 0;                      // an empty input is not an error (and has no pointers)
+    GF_REQUIRE(words && out, "null argument");
     gf::decode_tiles_kernel<<<(unsigned)((tiles + 7) / 8), 256, 0, (cudaStream_t)stream>>>(words, (long)tiles, (__half *)out);
     GF_CUDA(cudaGetLastError());
     return 0;

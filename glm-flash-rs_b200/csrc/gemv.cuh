@@ -129,14 +129,17 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     for (int m = 0; m < 16; ++m) nmem += rows_sh[m] >= 0;   // members come first
 
     // ---- stage the members' activations of this K range as (x_k, 0) pairs, permuted to the mma order:
-    //      dword position of local k = 64 g + 16 T + 8 h + 2 t + b  is  g*64 + (2t + h)*8 + 2T + b
+    //      dword position of local k = 64 g + 16 T + 8 h + 2 t + b  is  g*64 + (2t + h)*8 + 2T + b.
+    //      Rows of absent members are left as they are: an mma column depends on its own B column only, and the
+    //      columns of absent members are never stored.
     {
         const int k0 = kt0 * 16;
-        for (int i = tid; i < MATS * SETS * 8 * (GEMV_KC / 2); i += GEMV_THREADS) {
-            const int kp = i % (GEMV_KC / 2), m = (i / (GEMV_KC / 2)) % (SETS * 8), mat = i / ((GEMV_KC / 2) * SETS * 8);
+        const int items = MATS * nmem * (GEMV_KC / 2);
+#pragma unroll 4
+        for (int i = tid; i < items; i += GEMV_THREADS) {
+            const int kp = i % (GEMV_KC / 2), m = (i / (GEMV_KC / 2)) % nmem, mat = i / ((GEMV_KC / 2) * nmem);
             const int p = rows_sh[m];
-            uint32_t v = 0u;
-            if (p >= 0) v = __ldcg(reinterpret_cast<const uint32_t *>((mat ? a.X1 : a.X0) + (size_t)p * a.K + k0) + kp);
+            const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>((mat ? a.X1 : a.X0) + (size_t)p * a.K + k0) + kp);
             const int kl = 2 * kp;
             const int g = kl >> 6, TT = (kl >> 4) & 3, h = (kl >> 3) & 1, t = (kl >> 1) & 3;
             const int pos = g * 64 + (2 * t + h) * 8 + 2 * TT;
