@@ -53,6 +53,9 @@ SYMBOLS = {
     "glmflash_fast_experts_run": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I]),
     "glmflash_fast_experts_output": (_P, [_P]),
     "glmflash_fast_experts_xd": (_P, [_P]),
+    "glmflash_fast_experts_row_pairs": (_P, [_P]),
+    "glmflash_fast_experts_plan": (_P, [_P]),
+    "glmflash_fast_experts_status": (_P, [_P]),
     "glmflash_moe_new": (_I, [_P, _Z, _P]),
     "glmflash_moe_free": (None, [_P]),
     "glmflash_moe_run": (_I, [_P, _P, _P, _P, _I, _P, _P, _I]),
@@ -244,9 +247,25 @@ class FastExperts(_Owner):
 
     @property
     def xd(self):
+        """fp16 [grouped rows][I]; grouped row j is pair row_pairs[j] (valid rows: plan[1])."""
         import torch
         return _view(lib().glmflash_fast_experts_xd(self._h), (self.cfg.max_rows * self.cfg.slots, self.cfg.inter),
                      torch.float16)
+
+    @property
+    def row_pairs(self):
+        import torch
+        return _view(lib().glmflash_fast_experts_row_pairs(self._h), (self.cfg.max_rows * self.cfg.slots,), torch.int32)
+
+    @property
+    def plan(self):
+        import torch
+        return _view(lib().glmflash_fast_experts_plan(self._h), (2,), torch.int32)
+
+    @property
+    def status(self):
+        import torch
+        return _view(lib().glmflash_fast_experts_status(self._h), (1,), torch.int32)
 
 
 class Moe(_Owner):

@@ -1,14 +1,618 @@
-// FastExperts placeholder (replaced by the tcgen05 grouped GEMM).
-#include "common.cuh"
-struct glmflash_fast_experts { int unused; };
-extern "C" int glmflash_fast_experts_new(const glmflash_config *, size_t, glmflash_fast_experts **out) {
-    if (out) *out = nullptr;
-    return gf::fail("fast experts: not built yet");
+// FastExperts: the prefill owner (upstream src/fast_experts.rs:27-208) as two persistent grouped GEMMs on the
+// 5th-generation tensor cores (tcgen05.mma, accumulators in tensor memory), sm_100a only.
+//
+// Replaces upstream's fast_rot_in / fast_expert_plan / fast_gu_shared / fast_gu_separate / fast_down /
+// fast_down_large (native/exl3_prefill.cu:402-430,657-889), which decode each 16x16 trellis tile into mma.sync
+// fragments in registers.  Here:
+//
+//   plan      one block: members per distinct expert, 128-row M tiles per expert, and the GROUPED row order
+//             (rows of an expert contiguous): src_pair[j] = pair index of grouped row j.
+//   rot       the input rotation writes Xs[j] = fp16(H(x[row] * suh[e]) / sqrt 128) in grouped order, so the A
+//             operand of every M tile is a contiguous 128 x K slab that one TMA tensor load brings into shared
+//             memory in the 128-byte-swizzled K-major layout the tensor core reads.
+//   gemm      persistent CTAs, one per SM, walk work items (M tile, 128-column block) round robin.  Warp roles:
+//               warp 0      TMA producer of A stages (128 rows x 64 k)
+//               warp 1      issues tcgen05.mma (M 128 x N 128 x K 16, fp16 -> fp32), commits stages and tiles
+//               warp 2      allocates / frees tensor memory
+//               warps 4-7   epilogue: tcgen05.ld one accumulator row (128 fp32) per thread, so the 128-point
+//                           Hadamard transform of the column block runs in the thread's registers; scales, limited
+//                           SwiGLU, down-input rotation; stores fp16 Xd rows (gate/up) or fp32 Y rows (down)
+//               warps 8-15  decode trellis tiles of B (the weights) to fp16 straight into the swizzled K-major
+//                           shared-memory tile (bit-exact codebook; conflict-free 32-bit stores)
+//             A 3- (gate/up) or 6-stage (down) ring of 64-k stages and two accumulator buffers in tensor memory
+//             let the epilogue of one item overlap the main loop of the next.
+// Arithmetic: one full-K fp32 accumulation chain per output (as upstream's prefill path, which is likewise not
+// bit-equal to its decode path: native/exl3_prefill.cu:20-23), the same transforms and rounding points as
+// upstream's epilogue (native/exl3_prefill.cu:596-622 == native/exl3.cu:260-321).  Deterministic: static work
+// assignment, no atomics; every pair's result depends only on its own row.
+// Every wait is bounded; a wait that gives up raises the abort flag, every role leaves its loops, tensor memory
+// is freed and the status word reports the failure.
+#include <cuda.h>
+
+#include <algorithm>
+#include <new>
+
+#include "gemv.cuh"
+
+namespace gf {
+int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
+
+constexpr int FG_THREADS = 512;
+constexpr int FG_BM = 128, FG_BN = 128, FG_BK = 64;
+constexpr int FG_TILE_BYTES = FG_BM * FG_BK * 2;           // 16 KB: one 128 x 64 fp16 operand tile
+constexpr int FG_MAXU = 1024;
+
+// plan layout (int32): [0] total M tiles, [1] total grouped rows, [2 .. 2+MAXU] tile_base, [.. +MAXU+1] row_base
+constexpr int PLAN_TILE_BASE = 2, PLAN_ROW_BASE = 2 + FG_MAXU + 1, PLAN_INTS = 2 + 2 * (FG_MAXU + 1);
+
+// ---------------------------------------------------------------------------------------------- plan
+__global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restrict__ ids, const int *__restrict__ count,
+                                                          const int *__restrict__ members, int maxm, int slots, int E,
+                                                          int shared_exl3, int e_lo, int e_hi, int *__restrict__ plan,
+                                                          int *__restrict__ src_pair, int *__restrict__ row_expert) {
+    __shared__ int cnt_sh[FG_MAXU], row_sh[FG_MAXU], e_sh[FG_MAXU];
+    __shared__ int wsum[2][32];
+    const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
+    const int n = min(count[0], FG_MAXU);
+    int cnt = 0, e = -1;
+    if (u < n) {
+        e = ids[u];
+        if (!expert_skipped(e, E, shared_exl3, e_lo, e_hi)) {
+            const int *m = members + (size_t)u * maxm;
+            int lo = 0, hi = maxm;                          // members come first: the count is the first -1
+            while (lo < hi) {
+                const int mid = (lo + hi) >> 1;
+                if (m[mid] >= 0) lo = mid + 1; else hi = mid;
+            }
+            cnt = lo;
+        }
+    }
+    const int tiles = (cnt + FG_BM - 1) / FG_BM;
+    // block-wide exclusive scans of tiles and cnt
+    int t_inc = tiles, r_inc = cnt;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const int a = __shfl_up_sync(0xffffffffu, t_inc, d), b = __shfl_up_sync(0xffffffffu, r_inc, d);
+        if (lane >= d) { t_inc += a; r_inc += b; }
+    }
+    if (lane == 31) { wsum[0][warp] = t_inc; wsum[1][warp] = r_inc; }
+    __syncthreads();
+    int t_off = 0, r_off = 0, t_all = 0, r_all = 0;
+    for (int w = 0; w < 32; ++w) {
+        if (w < warp) { t_off += wsum[0][w]; r_off += wsum[1][w]; }
+        t_all += wsum[0][w]; r_all += wsum[1][w];
+    }
+    const int t_ex = t_off + t_inc - tiles, r_ex = r_off + r_inc - cnt;
+    cnt_sh[u] = cnt; row_sh[u] = r_ex; e_sh[u] = e;
+    plan[PLAN_TILE_BASE + u] = t_ex;
+    plan[PLAN_ROW_BASE + u] = r_ex;
+    if (u == 0) {
+        plan[0] = t_all; plan[1] = r_all;
+        plan[PLAN_TILE_BASE + FG_MAXU] = t_all;
+        plan[PLAN_ROW_BASE + FG_MAXU] = r_all;
+    }
+    __syncthreads();
+    for (int uu = 0; uu < n; ++uu) {
+        const int c = cnt_sh[uu], rb = row_sh[uu], ee = e_sh[uu];
+        for (int m = u; m < c; m += FG_MAXU) {
+            const int code = members[(size_t)uu * maxm + m];
+            src_pair[rb + m] = (code >> 5) * slots + (code & 31);
+            row_expert[rb + m] = ee;
+        }
+    }
 }
-extern "C" void glmflash_fast_experts_free(glmflash_fast_experts *) {}
-extern "C" int glmflash_fast_experts_run(glmflash_fast_experts *, void *, const glmflash_weights *, const void *, int,
-                                         const int32_t *, const int32_t *, const int32_t *, const int32_t *, int, int, int) {
-    return gf::fail("fast experts: not built yet");
+
+// ---------------------------------------------------------------------------------------------- rotation
+// One warp per (grouped row, 128-block, matrix).
+__global__ void __launch_bounds__(256) fast_rot_kernel(const __nv_bfloat16 *__restrict__ x, int x_stride,
+                                                       const int *__restrict__ plan, const int *__restrict__ src_pair,
+                                                       const int *__restrict__ row_expert, const __half *__restrict__ suh0,
+                                                       const __half *__restrict__ suh1, __half *__restrict__ out0,
+                                                       __half *__restrict__ out1, int K, int slots, int mats) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = K >> 7, rows = plan[1];
+    const long item = (long)blockIdx.x * 8 + warp;
+    if (item >= (long)rows * KB * mats) return;
+    const int blk = (int)(item % KB);
+    const int j = (int)((item / KB) % rows), mat = (int)(item / ((long)KB * rows));
+    const int p = src_pair[j], e = row_expert[j], row = p / slots;
+    const __half *suh = (mat ? suh1 : suh0) + (size_t)e * K + blk * 128 + 4 * lane;
+    const __nv_bfloat16 *xr = x + (size_t)row * x_stride + blk * 128 + 4 * lane;
+    float v[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __bfloat162float(xr[i]) * __half2float(suh[i]);
+    fwht128(v, lane);
+    __half *o = (mat ? out1 : out0) + (size_t)j * K + blk * 128 + 4 * lane;
+    __half2 h01 = __halves2half2(__float2half_rn(v[0] * HAD_SCALE), __float2half_rn(v[1] * HAD_SCALE));
+    __half2 h23 = __halves2half2(__float2half_rn(v[2] * HAD_SCALE), __float2half_rn(v[3] * HAD_SCALE));
+    *reinterpret_cast<uint2 *>(o) = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
 }
-extern "C" float *glmflash_fast_experts_output(const glmflash_fast_experts *) { return nullptr; }
-extern "C" const uint16_t *glmflash_fast_experts_xd(const glmflash_fast_experts *) { return nullptr; }
+
+// ---------------------------------------------------------------------------------------------- tcgen05 helpers
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t *slot_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(slot_smem)), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// D[tmem] (+)= A[smem desc] * B[smem desc]^T, M 128 x N 128 x K 16, fp16 operands, fp32 accumulate
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// arrive on an mbarrier when every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 consecutive fp32 columns of this thread's TMEM lane
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float *v) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major, 128-byte swizzle: rows of 128 bytes, 8-row groups 1024 bytes apart; the tile base is 1024-aligned and
+// a K step of 16 halves advances the start address by 32 bytes inside the swizzle atom.
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFFu);          // start address
+    d |= (uint64_t)1 << 16;                               // leading byte offset (unused with swizzle): 16 B
+    d |= (uint64_t)(1024 >> 4) << 32;                     // stride byte offset: 8 rows x 128 B
+    d |= (uint64_t)1 << 46;                               // descriptor version of sm_100
+    d |= (uint64_t)2 << 61;                               // SWIZZLE_128B
+    return d;
+}
+// kind::f16: D fp32, A and B fp16, both K-major, N 128, M 128
+constexpr uint32_t UMMA_IDESC = (1u << 4) | ((uint32_t)(FG_BN >> 3) << 17) | ((uint32_t)(FG_BM >> 4) << 24);
+
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+// Wait on an mbarrier phase, giving up when the abort flag is up or after a bounded number of polls.
+__device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
+    for (uint32_t i = 0; i < 20000000u; ++i) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 63u) == 63u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    atomicExch(status, code);
+    return false;
+}
+
+// In-register 128-point Walsh-Hadamard transform, butterflies stride 1..64, (lower + upper, lower - upper):
+// upstream's order (native/exl3.cu:208-219), so every sum associates as there.
+__device__ __forceinline__ void fwht128_regs(float (&v)[128]) {
+#pragma unroll
+    for (int s = 1; s < 128; s <<= 1)
+#pragma unroll
+        for (int i = 0; i < 128; ++i)
+            if (!(i & s)) {
+                const float a = v[i], b = v[i | s];
+                v[i] = a + b;
+                v[i | s] = a - b;
+            }
+}
+
+struct FastGemmArgs {
+    const uint32_t *T0, *T1;       // trellis banks
+    const int *ids, *plan, *src_pair;
+    const __half *sv0, *sv1, *sd;  // gate/up: svh_g, svh_u, suh_d;  down: svh_d
+    __half *xd;                    // gate/up out, grouped rows [rows][N]
+    float *y;                      // down out, pair rows [P][N]
+    int *status;
+    int K, N, shared_x;
+    float limit;
+};
+
+struct TileInfo {
+    int u, e, row0, cnt, nb;
+};
+__device__ __forceinline__ TileInfo tile_info(int item, int NB, const int *tile_base, const int *row_base, const int *ids, int maxu) {
+    TileInfo t;
+    const int mt = item / NB;
+    t.nb = item % NB;
+    int lo = 0, hi = maxu;                                 // largest u with tile_base[u] <= mt
+    while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if (tile_base[mid] <= mt) lo = mid; else hi = mid;
+    }
+    // experts without tiles share a base with their successor: step to the last one that starts at or before mt
+    t.u = lo;
+    t.e = ids[lo];
+    t.row0 = row_base[lo] + (mt - tile_base[lo]) * FG_BM;
+    t.cnt = min(FG_BM, row_base[lo + 1] - t.row0);
+    return t;
+}
+
+template <int MATS>
+struct FgCfg {
+    static constexpr int STAGES = MATS == 2 ? 3 : 6;
+    static constexpr int STAGE_BYTES = MATS == 2 ? 4 * FG_TILE_BYTES : 2 * FG_TILE_BYTES;   // A0 A1 B0 B1 | A0 B0
+    static constexpr int TMEM_COLS = MATS == 2 ? 512 : 256;                                  // 2 buffers of MATS x 128 columns
+    static constexpr size_t SMEM = 1024 /*align*/ + (size_t)STAGES * STAGE_BYTES + 8192 /*tables*/;
+};
+
+template <int MATS>
+__global__ void __launch_bounds__(FG_THREADS, 1)
+fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constant__ CUtensorMap mapA1, const FastGemmArgs a) {
+    using C = FgCfg<MATS>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-aligned operand tiles
+    unsigned char *stages = smem;
+    unsigned char *tables = smem + (size_t)C::STAGES * C::STAGE_BYTES;
+    uint64_t *full = reinterpret_cast<uint64_t *>(tables);                 // [STAGES] A landed (tx) + 8 decode warps
+    uint64_t *empty = full + C::STAGES;                                    // [STAGES] MMAs of the stage completed
+    uint64_t *tmem_full = empty + C::STAGES;                               // [2] accumulator complete
+    uint64_t *tmem_empty = tmem_full + 2;                                  // [2] accumulator drained (4 epilogue warps)
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    float *scales = reinterpret_cast<float *>(tables + 256);               // [3][128]
+    int *tile_base = reinterpret_cast<int *>(tables + 256 + 3 * 128 * 4);  // [maxu + 1] (<= 1025 ints), then row_base
+    const int maxu = FG_MAXU;
+    int *row_base = nullptr;                                               // read from global (L1/L2 hits): keeps smem small
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int KT = a.K >> 4, NTILES = a.N >> 4, NB = a.N >> 7, KS = a.K / FG_BK;
+    const int total = a.plan[0] * NB;
+
+    if (tid == 0) {
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full + s, 9); mbar_init(empty + s, 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tmem_full + b, 1); mbar_init(tmem_empty + b, 4); }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    for (int i = tid; i <= maxu; i += FG_THREADS) tile_base[i] = a.plan[PLAN_TILE_BASE + i];
+    row_base = const_cast<int *>(a.plan) + PLAN_ROW_BASE;
+    if (warp == 2) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp < 4) {
+        // ------------------------------------------------------------------ warpgroup 0: TMA, MMA issue
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+        if (warp == 0 && lane == 0) {
+            uint32_t it = 0;
+            for (int item = blockIdx.x; item < total && !*abort_flag; item += gridDim.x) {
+                const TileInfo t = tile_info(item, NB, tile_base, row_base, a.ids, maxu);
+                for (int s = 0; s < KS; ++s, ++it) {
+                    const int slot = it % C::STAGES;
+                    const uint32_t n = it / C::STAGES;
+                    if (!wait_or_abort(empty + slot, (n & 1) ^ 1, abort_flag, a.status, GF_STATUS_TMA_TIMEOUT)) break;
+                    unsigned char *st = stages + (size_t)slot * C::STAGE_BYTES;
+                    const bool two = MATS == 2 && !a.shared_x;
+                    mbar_expect_tx(full + slot, (two ? 2 : 1) * FG_TILE_BYTES);
+                    tma_load_2d(st, &mapA0, s * FG_BK, t.row0, full + slot);
+                    if (two) tma_load_2d(st + FG_TILE_BYTES, &mapA1, s * FG_BK, t.row0, full + slot);
+                }
+            }
+        } else if (warp == 1 && lane == 0) {
+            uint32_t it = 0, ti = 0;
+            for (int item = blockIdx.x; item < total && !*abort_flag; item += gridDim.x, ++ti) {
+                const uint32_t buf = ti & 1;
+                if (!wait_or_abort(tmem_empty + buf, ((ti >> 1) & 1) ^ 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) break;
+                tc_fence_after();
+                const uint32_t d0 = tmem_base + buf * (MATS * FG_BN);
+                bool ok = true;
+                for (int s = 0; s < KS; ++s, ++it) {
+                    const int slot = it % C::STAGES;
+                    const uint32_t n = it / C::STAGES;
+                    if (!wait_or_abort(full + slot, n & 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(stages + (size_t)slot * C::STAGE_BYTES);
+                    const uint32_t a0 = sa, a1 = (MATS == 2 && !a.shared_x) ? sa + FG_TILE_BYTES : sa;
+                    const uint32_t b0 = sa + (MATS == 2 ? 2 : 1) * FG_TILE_BYTES, b1 = b0 + FG_TILE_BYTES;
+#pragma unroll
+                    for (int kk = 0; kk < FG_BK / 16; ++kk) {
+                        const uint32_t acc = (s > 0 || kk > 0) ? 1u : 0u;
+                        umma_f16(d0, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32), UMMA_IDESC, acc);
+                        if (MATS == 2)
+                            umma_f16(d0 + FG_BN, umma_desc_sw128(a1 + kk * 32), umma_desc_sw128(b1 + kk * 32), UMMA_IDESC, acc);
+                    }
+                    umma_commit(empty + slot);              // the stage may be overwritten once these MMAs have read it
+                }
+                if (!ok) break;
+                umma_commit(tmem_full + buf);               // the accumulators of this item are complete
+            }
+        }
+    } else if (warp < 8) {
+        // ------------------------------------------------------------------ warpgroup 1: epilogue
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
+        const int q = warp & 3, m = q * 32 + lane;           // TMEM lane == row of the M tile
+        uint32_t ti = 0;
+        for (int item = blockIdx.x; item < total; item += gridDim.x, ++ti) {
+            const TileInfo t = tile_info(item, NB, tile_base, row_base, a.ids, maxu);
+            const uint32_t buf = ti & 1;
+            // scale vectors of (expert, column block): one element per thread, shared by the 128 epilogue threads
+            asm volatile("bar.sync 1, 128;");
+            {
+                const size_t o = (size_t)t.e * a.N + t.nb * 128 + m;
+                scales[m] = __half2float(a.sv0[o]);
+                if (MATS == 2) { scales[128 + m] = __half2float(a.sv1[o]); scales[256 + m] = __half2float(a.sd[o]); }
+            }
+            asm volatile("bar.sync 1, 128;");
+            if (!wait_or_abort(tmem_full + buf, (ti >> 1) & 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) break;
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MATS * FG_BN);
+            float v[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld32(taddr + c * 32, v + c * 32);
+            tmem_ld_wait();
+            if (MATS == 2) {
+                uint32_t gpk[64];                            // gate after scale / bf16 rounding / clamp, two per register
+                fwht128_regs(v);
+#pragma unroll
+                for (int i = 0; i < 64; ++i) {
+                    const float g0 = fminf(bf16r(v[2 * i] * HAD_SCALE * scales[2 * i]), a.limit);
+                    const float g1 = fminf(bf16r(v[2 * i + 1] * HAD_SCALE * scales[2 * i + 1]), a.limit);
+                    gpk[i] = (__float_as_uint(g0) >> 16) | (__float_as_uint(g1) & 0xffff0000u);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(taddr + FG_BN + c * 32, v + c * 32);
+                tmem_ld_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty + buf);            // both accumulators are in registers
+                fwht128_regs(v);
+#pragma unroll
+                for (int i = 0; i < 128; ++i) {
+                    const float gg = __uint_as_float((i & 1) ? (gpk[i >> 1] & 0xffff0000u) : (gpk[i >> 1] << 16));
+                    const float uu = fminf(fmaxf(bf16r(v[i] * HAD_SCALE * scales[128 + i]), -a.limit), a.limit);
+                    const float act = bf16r(bf16r(gg / (1.f + expf(-gg))) * uu);
+                    v[i] = act * scales[256 + i];
+                }
+                fwht128_regs(v);
+                if (m < t.cnt) {
+                    uint4 *o = reinterpret_cast<uint4 *>(a.xd + (size_t)(t.row0 + m) * a.N + t.nb * 128);
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        __half2 h[4];
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            h[j] = __halves2half2(__float2half_rn(v[8 * c + 2 * j] * HAD_SCALE),
+                                                  __float2half_rn(v[8 * c + 2 * j + 1] * HAD_SCALE));
+                        o[c] = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
+                                          *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
+                    }
+                }
+            } else {
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(tmem_empty + buf);
+                fwht128_regs(v);
+                if (m < t.cnt) {
+                    const int p = a.src_pair[t.row0 + m];
+                    float4 *o = reinterpret_cast<float4 *>(a.y + (size_t)p * a.N + t.nb * 128);
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        o[c] = make_float4(v[4 * c] * HAD_SCALE * scales[4 * c], v[4 * c + 1] * HAD_SCALE * scales[4 * c + 1],
+                                           v[4 * c + 2] * HAD_SCALE * scales[4 * c + 2], v[4 * c + 3] * HAD_SCALE * scales[4 * c + 3]);
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ warpgroups 2-3: trellis decode of B
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+        const int dw = warp - 8;
+        constexpr int NTL = MATS == 2 ? 8 : 4;               // n tiles of this warp per stage
+        const int mat = MATS == 2 ? (dw >> 2) : 0;
+        const int ktl = dw & 3;
+        const int nt_begin = MATS == 2 ? 0 : (dw >> 2) * 4;
+        const int g = lane >> 2, tq = lane & 3;
+        const uint32_t *Tm = mat ? a.T1 : a.T0;
+        // byte offsets inside a B tile of this lane's four 32-bit stores (before the n-tile offset)
+        const int c0 = 2 * ktl, c1 = 2 * ktl + 1;
+        const int off_lo0 = g * 128 + ((c0 ^ g) << 4) + 4 * tq;            // n = g,     k = 2t
+        const int off_lo1 = g * 128 + ((c1 ^ g) << 4) + 4 * tq;            // n = g,     k = 2t + 8
+        const int off_hi0 = off_lo0 + 8 * 128, off_hi1 = off_lo1 + 8 * 128; // n = g + 8 (same n & 7)
+        uint32_t it = 0;
+        uint32_t wcur[NTL], wnext[NTL];
+        int item = blockIdx.x;
+        auto load_words = [&](const TileInfo &t, int s, uint32_t (&w)[NTL]) {
+            const uint32_t *src = Tm + (((size_t)t.e * KT + 4 * s + ktl) * NTILES + (size_t)t.nb * 8 + nt_begin) * 32 + lane;
+#pragma unroll
+            for (int i = 0; i < NTL; ++i) w[i] = __ldg(src + i * 32);
+        };
+        TileInfo t{};
+        if (item < total) {
+            t = tile_info(item, NB, tile_base, row_base, a.ids, maxu);
+            load_words(t, 0, wcur);
+        }
+        while (item < total && !*abort_flag) {
+            const int next_item = item + gridDim.x;
+            TileInfo tn{};
+            if (next_item < total) tn = tile_info(next_item, NB, tile_base, row_base, a.ids, maxu);
+            bool ok = true;
+            for (int s = 0; s < KS; ++s, ++it) {
+                if (s + 1 < KS) load_words(t, s + 1, wnext);
+                else if (next_item < total) load_words(tn, 0, wnext);
+                const int slot = it % C::STAGES;
+                const uint32_t n = it / C::STAGES;
+                if (!wait_or_abort(empty + slot, (n & 1) ^ 1, abort_flag, a.status, GF_STATUS_TMA_TIMEOUT)) { ok = false; break; }
+                unsigned char *bt = stages + (size_t)slot * C::STAGE_BYTES + (MATS == 2 ? 2 + mat : 1) * FG_TILE_BYTES +
+                                    nt_begin * 16 * 128;
+#pragma unroll
+                for (int i = 0; i < NTL; ++i) {
+                    const uint32_t w = wcur[i];
+                    const uint32_t pw = __shfl_sync(0xffffffffu, w, (lane + 31) & 31);
+                    uint32_t x0, x1, x2, x3, x4, x5, x6, x7;
+                    codeword_pair(__funnelshift_r(w, pw, 12), x0, x4);     // j = 0 | 4
+                    codeword_pair(__funnelshift_r(w, pw, 8), x1, x5);      // j = 1 | 5
+                    codeword_pair(__funnelshift_r(w, pw, 4), x2, x6);      // j = 2 | 6
+                    codeword_pair(w, x3, x7);                              // j = 3 | 7
+                    const uint32_t p01 = __byte_perm(weight_dup(x0), weight_dup(x1), 0x5410);
+                    const uint32_t p23 = __byte_perm(weight_dup(x2), weight_dup(x3), 0x5410);
+                    const uint32_t p45 = __byte_perm(weight_dup(x4), weight_dup(x5), 0x5410);
+                    const uint32_t p67 = __byte_perm(weight_dup(x6), weight_dup(x7), 0x5410);
+                    unsigned char *tb = bt + i * 16 * 128;
+                    *reinterpret_cast<uint32_t *>(tb + off_lo0) = p01;
+                    *reinterpret_cast<uint32_t *>(tb + off_lo1) = p23;
+                    *reinterpret_cast<uint32_t *>(tb + off_hi0) = p45;
+                    *reinterpret_cast<uint32_t *>(tb + off_hi1) = p67;
+                }
+                fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
+                __syncwarp();
+                if (lane == 0) mbar_arrive(full + slot);
+#pragma unroll
+                for (int i = 0; i < NTL; ++i) wcur[i] = wnext[i];
+            }
+            if (!ok) break;
+            item = next_item;
+            t = tn;
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 2) tmem_dealloc(tmem_base, C::TMEM_COLS);
+}
+
+}  // namespace gf
+
+using namespace gf;
+
+// ---------------------------------------------------------------------------------------------- host side
+namespace {
+int fail_if(cudaError_t e) { return e == cudaSuccess ? 0 : gf::fail_cuda(e, "cudaFuncSetAttribute"); }
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                                  const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// fp16 matrix [rows][K] row-major; box = 128 rows x 64 halves (128 bytes), 128-byte swizzle
+int make_map(CUtensorMap *map, void *base, uint64_t rows, uint64_t K) {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        GF_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+        GF_REQUIRE(p != nullptr && q == cudaDriverEntryPointSuccess, "cuTensorMapEncodeTiled is not available in this driver");
+        fn = (EncodeTiledFn)p;
+    }
+    const cuuint64_t dims[2] = {K, rows};
+    const cuuint64_t strides[1] = {K * 2};
+    const cuuint32_t box[2] = {FG_BK, FG_BM};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    GF_REQUIRE(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+    return 0;
+}
+}  // namespace
+
+struct glmflash_fast_experts {
+    glmflash_config cfg;
+    __half *xg = nullptr, *xu = nullptr, *xd = nullptr;     // grouped rows
+    float *out = nullptr;                                   // pair rows
+    int *plan = nullptr, *src_pair = nullptr, *row_expert = nullptr, *status = nullptr;
+    CUtensorMap map_xg, map_xu, map_xd;
+    int sms = 0;
+};
+
+extern "C" int glmflash_fast_experts_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_fast_experts **out) {
+    GF_REQUIRE(out != nullptr, "out is null");
+    *out = nullptr;
+    if (check_config(cfg, cfg_bytes, 8192)) return -1;       // upstream: 1..=8192 rows, src/fast_experts.rs:44-47
+    GF_REQUIRE(cfg->experts + 1 <= FG_MAXU, "too many experts for the prefill plan");
+    glmflash_fast_experts *f = new (std::nothrow) glmflash_fast_experts();
+    GF_REQUIRE(f != nullptr, "out of host memory");
+    f->cfg = *cfg;
+    const size_t H = cfg->hidden, I = cfg->inter, P = (size_t)cfg->max_rows * cfg->slots;
+    auto alloc = [&](void **p, size_t bytes) -> int {
+        GF_CUDA(cudaMalloc(p, bytes));
+        GF_CUDA(cudaMemset(*p, 0, bytes));
+        return 0;
+    };
+    int dev = 0;
+    cudaDeviceProp prop;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) {
+        delete f;
+        return fail("cannot query the CUDA device");
+    }
+    f->sms = prop.multiProcessorCount;
+    if (prop.major != 10) {
+        delete f;
+        return fail("the prefill path needs an sm_100 GPU (tcgen05 / tensor memory)");
+    }
+    if (alloc((void **)&f->xg, P * H * 2) || alloc((void **)&f->xu, P * H * 2) || alloc((void **)&f->xd, P * I * 2) ||
+        alloc((void **)&f->out, P * H * 4) || alloc((void **)&f->plan, PLAN_INTS * 4) || alloc((void **)&f->src_pair, P * 4) ||
+        alloc((void **)&f->row_expert, P * 4) || alloc((void **)&f->status, 4) || make_map(&f->map_xg, f->xg, P, H) ||
+        make_map(&f->map_xu, f->xu, P, H) || make_map(&f->map_xd, f->xd, P, I) ||
+        fail_if(cudaFuncSetAttribute(fast_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FgCfg<2>::SMEM)) ||
+        fail_if(cudaFuncSetAttribute(fast_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FgCfg<1>::SMEM))) {
+        glmflash_fast_experts_free(f);
+        return -1;
+    }
+    *out = f;
+    return 0;
+}
+
+extern "C" void glmflash_fast_experts_free(glmflash_fast_experts *f) {
+    if (!f) return;
+    cudaFree(f->xg); cudaFree(f->xu); cudaFree(f->xd); cudaFree(f->out); cudaFree(f->plan); cudaFree(f->src_pair);
+    cudaFree(f->row_expert); cudaFree(f->status);
+    delete f;
+}
+
+extern "C" int glmflash_fast_experts_run(glmflash_fast_experts *f, void *stream, const glmflash_weights *w, const void *input,
+                                         int x_stride, const int32_t *picks, const int32_t *ids, const int32_t *count,
+                                         const int32_t *members, int rows, int maxm, int shared_x) {
+    GF_REQUIRE(f && w && input && picks && ids && count && members, "null argument");
+    const glmflash_config &c = f->cfg;
+    GF_REQUIRE(rows > 0 && rows <= c.max_rows && maxm >= rows && maxm <= c.max_rows, "expert rows/member stride outside scratch");
+    GF_REQUIRE(x_stride >= c.hidden && x_stride % 4 == 0, "x_stride must be >= hidden and a multiple of 4");
+    GF_REQUIRE(((uintptr_t)w->gt | (uintptr_t)w->ut | (uintptr_t)w->dt) % 16 == 0, "trellis tensors must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
+    const int H = c.hidden, I = c.inter;
+    const long P = (long)rows * c.slots;
+    fast_plan_kernel<<<1, FG_MAXU, 0, s>>>(ids, count, members, maxm, c.slots, c.experts, c.shared_exl3, c.expert_lo, c.expert_hi,
+                                          f->plan, f->src_pair, f->row_expert);
+    GF_CUDA(cudaGetLastError());
+    const int mats = shared_x ? 1 : 2;
+    const long items = P * (H / 128) * mats;
+    fast_rot_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>((const __nv_bfloat16 *)input, x_stride, f->plan, f->src_pair,
+                                                              f->row_expert, (const __half *)w->suh_g, (const __half *)w->suh_u,
+                                                              f->xg, f->xu, H, c.slots, mats);
+    GF_CUDA(cudaGetLastError());
+    FastGemmArgs a{};
+    a.ids = ids; a.plan = f->plan; a.src_pair = f->src_pair; a.status = f->status; a.limit = c.limit;
+    a.T0 = w->gt; a.T1 = w->ut; a.sv0 = (const __half *)w->svh_g; a.sv1 = (const __half *)w->svh_u; a.sd = (const __half *)w->suh_d;
+    a.xd = f->xd; a.y = nullptr; a.K = H; a.N = I; a.shared_x = shared_x ? 1 : 0;
+    fast_gemm_kernel<2><<<f->sms, FG_THREADS, FgCfg<2>::SMEM, s>>>(f->map_xg, f->map_xu, a);
+    GF_CUDA(cudaGetLastError());
+    a.T0 = w->dt; a.T1 = w->dt; a.sv0 = (const __half *)w->svh_d; a.sv1 = nullptr; a.sd = nullptr;
+    a.xd = nullptr; a.y = f->out; a.K = I; a.N = H; a.shared_x = 1;
+    fast_gemm_kernel<1><<<f->sms, FG_THREADS, FgCfg<1>::SMEM, s>>>(f->map_xd, f->map_xd, a);
+    GF_CUDA(cudaGetLastError());
+    return 0;
+}
+
+extern "C" float *glmflash_fast_experts_output(const glmflash_fast_experts *f) { return f ? f->out : nullptr; }
+extern "C" const uint16_t *glmflash_fast_experts_xd(const glmflash_fast_experts *f) { return f ? (const uint16_t *)f->xd : nullptr; }
+extern "C" const int32_t *glmflash_fast_experts_row_pairs(const glmflash_fast_experts *f) { return f ? f->src_pair : nullptr; }
+extern "C" const int32_t *glmflash_fast_experts_plan(const glmflash_fast_experts *f) { return f ? f->plan : nullptr; }
+extern "C" const int32_t *glmflash_fast_experts_status(const glmflash_fast_experts *f) { return f ? f->status : nullptr; }

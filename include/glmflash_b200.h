@@ -125,8 +125,16 @@ void glmflash_fast_experts_free(glmflash_fast_experts *f);
 int  glmflash_fast_experts_run(glmflash_fast_experts *f, void *stream, const glmflash_weights *w,
                                const void *input, int x_stride, const int32_t *picks, const int32_t *ids,
                                const int32_t *count, const int32_t *members, int rows, int maxm, int shared_x);
-float *glmflash_fast_experts_output(const glmflash_fast_experts *f);       /* fp32 [rows*slots][H] */
-const uint16_t *glmflash_fast_experts_xd(const glmflash_fast_experts *f);  /* fp16 [rows*slots][I] */
+float *glmflash_fast_experts_output(const glmflash_fast_experts *f);       /* fp32 [rows*slots][H], pair order */
+/* Down-projection inputs of the last run, fp16 [grouped rows][I].  The prefill path keeps its intermediate rows
+ * GROUPED (the rows of an expert are contiguous, experts in ascending id order, so that an M tile is one TMA
+ * tensor load); grouped row j belongs to pair glmflash_fast_experts_row_pairs()[j]; the number of grouped rows
+ * is plan[1], the number of 128-row M tiles plan[0]. */
+const uint16_t *glmflash_fast_experts_xd(const glmflash_fast_experts *f);
+const int32_t *glmflash_fast_experts_row_pairs(const glmflash_fast_experts *f);
+const int32_t *glmflash_fast_experts_plan(const glmflash_fast_experts *f);
+/* Device status word, as glmflash_experts_status. */
+const int32_t *glmflash_fast_experts_status(const glmflash_fast_experts *f);
 
 /* ---- Moe: the whole layer after routing  (src/moe.rs:11-182, src/batch.rs:1160-1210) ---------------- */
 typedef struct glmflash_moe glmflash_moe;
