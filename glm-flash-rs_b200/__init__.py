@@ -35,6 +35,8 @@ SYMBOLS = {
     "glmflash_exl3_decode": (_I, [_P, _P, C.c_int64, _P]),
     "glmflash_exl3_linear_scratch_bytes": (_Z, [_I, _I]),
     "glmflash_exl3_linear": (_I, [_P, _P, _I, _P, _P, _P, _I, _I, _P, _P]),
+    "glmflash_exl3_linear_static_max_bytes": (_Z, []),
+    "glmflash_exl3_linear_static": (_I, [_P, _P, _I, _P, _P, _P, _I, _I, _P]),
     "glmflash_grouping_new": (_I, [_P, _Z, _P]),
     "glmflash_grouping_free": (None, [_P]),
     "glmflash_grouping_run": (_I, [_P, _P, _P, _I]),
@@ -154,6 +156,17 @@ def exl3_linear(x, words, suh, svh, K, N, stream=None):
     _check(lib().glmflash_exl3_linear(_stream_ptr(stream), x.data_ptr(), rows, words.data_ptr(), suh.data_ptr(),
                                       svh.data_ptr(), K, N, y.data_ptr(), scratch.data_ptr()))
     torch.cuda.current_stream().synchronize()      # scratch is freed on return
+    return y
+
+
+def exl3_linear_static(x, words, suh, svh, K, N, stream=None):
+    """exl3_linear without any allocation inside the library: the scratch is the library's built-in array
+    (K <= 2048, N <= 2048).  Calls that overlap on the GPU share that array and must be ordered by the caller."""
+    torch = _torch()
+    rows = x.shape[0]
+    y = torch.empty((rows, N), dtype=torch.float16, device=x.device)
+    _check(lib().glmflash_exl3_linear_static(_stream_ptr(stream), x.data_ptr(), rows, words.data_ptr(), suh.data_ptr(),
+                                             svh.data_ptr(), K, N, y.data_ptr()))
     return y
 
 

@@ -211,3 +211,38 @@ extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, c
     a.shared_exl3 = 1; a.mode = GEMV_LINEAR; a.limit = 10.f;
     return launch_gemv(s, 1, a, 1);
 }
+
+// ---- the single EXL3 linear for callers that must not allocate ------------------------------------------------
+// Same computation as glmflash_exl3_linear, but the scratch lives in a fixed array inside the library image instead
+// of caller-provided memory.  It is meant for hosts that own the whole device heap themselves (upstream's Rust
+// `Device` hands out every byte of device memory at start-up and keeps the request path free of allocator calls),
+// and for latency-critical loops in which a cudaMalloc/cudaFree would serialise the device behind the allocator.
+// The array is part of every loaded copy of the library: each GPU that loads it holds these bytes until exit.
+namespace {
+constexpr int STATIC_LINEAR_MAX_K = 2048, STATIC_LINEAR_MAX_N = 2048;
+constexpr size_t STATIC_LINEAR_BYTES = 1179648;           // 1.125 MiB >= linear_layout(2048, 2048).total
+static __device__ __align__(256) unsigned char g_static_linear_scratch[STATIC_LINEAR_BYTES];
+void *g_static_linear_ptr[64] = {};                       // device address of the array, per device ordinal
+}  // namespace
+
+extern "C" size_t glmflash_exl3_linear_static_max_bytes(void) { return STATIC_LINEAR_BYTES; }
+
+extern "C" int glmflash_exl3_linear_static(void *stream, const uint16_t *x, int rows, const uint32_t *words,
+                                           const uint16_t *suh, const uint16_t *svh, int K, int N, uint16_t *y) {
+    GF_REQUIRE(K > 0 && K % 256 == 0 && N > 0 && N % 128 == 0, "K must be a multiple of 256 and N of 128");
+    GF_REQUIRE(K <= STATIC_LINEAR_MAX_K && N <= STATIC_LINEAR_MAX_N,
+               "shape exceeds the built-in scratch (K <= 2048, N <= 2048): use glmflash_exl3_linear with caller scratch");
+    GF_REQUIRE(linear_layout(K, N).total <= STATIC_LINEAR_BYTES, "shape exceeds the built-in scratch");
+    int dev = 0;
+    GF_CUDA(cudaGetDevice(&dev));
+    GF_REQUIRE(dev >= 0 && dev < 64, "device ordinal out of range");
+    if (!g_static_linear_ptr[dev]) {
+        // In host code the array's name is only a handle; the address a kernel can use comes from the runtime,
+        // once per device, with that device current.
+        void *p = nullptr;
+        GF_CUDA(cudaGetSymbolAddress(&p, g_static_linear_scratch));
+        GF_REQUIRE(p != nullptr, "cudaGetSymbolAddress returned a null address");
+        g_static_linear_ptr[dev] = p;
+    }
+    return glmflash_exl3_linear(stream, x, rows, words, suh, svh, K, N, y, g_static_linear_ptr[dev]);
+}

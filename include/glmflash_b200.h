@@ -83,6 +83,20 @@ size_t glmflash_exl3_linear_scratch_bytes(int K, int N);
 int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, const uint32_t *words, const uint16_t *suh,
                          const uint16_t *svh, int K, int N, uint16_t *y, void *scratch);
 
+/* The same linear for callers that cannot allocate device memory.  This entry point has no counterpart in the
+ * reference.  It exists for hosts that took over the whole device heap at start-up (so a later cudaMalloc by a
+ * library would fail or fragment their pool) and for serving loops where an allocator call would stall every
+ * stream of the device.  The scratch is a fixed array inside the library (glmflash_exl3_linear_static_max_bytes(),
+ * 1.125 MiB, held by every GPU that loads the library until the process exits), so shapes are limited to
+ * K <= 2048 and N <= 2048; larger shapes are rejected with an error.  The call itself allocates nothing.
+ * The first call on a device looks up the array's device address (a one-time, per-device set-up step): make that
+ * first call outside any stream capture.  All calls share the one array and it keeps the previous call's
+ * contents; the call clears what has to start at zero, but two calls that overlap on the GPU (different streams
+ * without ordering, or different host threads) race on it: order them. */
+size_t glmflash_exl3_linear_static_max_bytes(void);
+int glmflash_exl3_linear_static(void *stream, const uint16_t *x, int rows, const uint32_t *words, const uint16_t *suh,
+                                const uint16_t *svh, int K, int N, uint16_t *y);
+
 /* ---- Grouping  (src/grouping.rs:29-111; kernels native/grouping.cu) --------------------------------- */
 typedef struct glmflash_grouping glmflash_grouping;
 int  glmflash_grouping_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_grouping **out);
