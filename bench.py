@@ -149,11 +149,159 @@ def run_reference(args, rank):
 
 
 def workload_config(args):
+    if args.workload == "prefill":
+        return {"workload": f"moe_layer_prefill_{args.rows}tok (config 4): uniform random top-4 routing, alternating over "
+                            f"{args.layers} layers of distinct weights", "hidden": H, "intermediate": I, "experts": E,
+                "shared_experts": 1, "top_k": S - 1, "bits_per_weight": 4, "rows": args.rows, "layers": args.layers,
+                "l2": "one layer's bank (308 MB) plus rotated activations exceed L2", "parallelism": f"ep{args.gpus}"}
     return {"workload": f"moe_layer_decode_bs{args.rows} (config 2{'/3' if args.rows > 1 else ''}) over a {args.layers}-layer stack of distinct "
                         "weights (config 5 stack)", "hidden": H, "intermediate": I, "experts": E, "shared_experts": 1, "top_k": S - 1,
             "bits_per_weight": 4, "rows": args.rows, "layers": args.layers,
             "l2": f"weights of a step ({args.layers} layers) exceed L2; every layer has its own weights",
             "parallelism": f"ep{args.gpus}"}
+
+
+def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
+    """Config 4: one step = one prefill chunk of `rows` tokens through one MoE layer (alternating layers)."""
+    R, L, G = args.rows, args.layers, world
+    banks = [synth.device_bank(1000 * l + 1, H, I, E, dev) for l in range(L)]
+    structs = [pkg.weights_struct(b) for b in banks]
+    xs = np.stack([synth.activations_bf16(9000 + l, R, H) for l in range(L)])
+    routes = [synth.route(9100 + l, R, E, S - 1, uniform=True) for l in range(L)]
+    ps, ws = np.stack([r[0] for r in routes]), np.stack([r[1] for r in routes])
+    x_d = torch.from_numpy(xs.view(np.int16)).to(dev).view(torch.bfloat16)
+    p_d, w_d = torch.from_numpy(ps).to(dev), torch.from_numpy(ws).to(dev)
+    lo, hi = rank * (E // G), (rank + 1) * (E // G)
+    # the shared expert's 4096 rows go to one rank per layer (round robin)
+    moes = {sh: pkg.Moe(pkg.make_config(H, I, E, S, max_rows=R, shared_exl3=sh, expert_lo=lo, expert_hi=hi))
+            for sh in ((0, 1) if G > 1 else (1,))}
+    owner = lambda l: moes[1 if (G == 1 or l % G == rank) else 0]
+    if G > 1:
+        gathered = torch.empty((G, R, H), dtype=torch.float32, device=dev)
+        final = torch.empty((R, H), dtype=torch.float32, device=dev)
+    stream = torch.cuda.Stream()
+    state = {"i": 0}
+
+    def step():
+        l = state["i"] % L
+        state["i"] += 1
+        m = owner(l)
+        m.run(structs[l], x_d[l], p_d[l], w_d[l], R)
+        if G > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
+            pkg.rank_sum(gathered, final)
+
+    def timed(fn, steps, warmup):
+        with torch.cuda.stream(stream):
+            for _ in range(warmup):
+                fn()
+            stream.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+        ms = e0.elapsed_time(e1) / steps
+        if world > 1:
+            t = torch.tensor([ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms_step = timed(step, args.steps, args.warmup)
+    clocks = sampler.stop() if rank == 0 else None
+    flops = R * S * 3 * 2 * H * I                                  # all pairs incl. the shared expert, three matrices
+    xh = torch.from_numpy(xs.view(np.int16)).pin_memory()
+    ph, wh = torch.from_numpy(ps).pin_memory(), torch.from_numpy(ws).pin_memory()
+    oh = torch.empty((R, H), dtype=torch.float32).pin_memory()
+
+    def step_e2e():
+        l = state["i"] % L
+        state["i"] += 1
+        m = owner(l)
+        m.run_host(structs[l], xh[l], ph[l], wh[l], R, oh, stream=stream)
+        if G > 1:
+            dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
+            pkg.rank_sum(gathered, final, stream=stream)
+            oh.copy_(final, non_blocking=True)
+            stream.synchronize()
+    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3)
+    e2e = {"value": R / (ms_e2e / 1e3), "unit": "layer-tokens/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": R * H * 2 + 2 * R * S * 4, "d2h_bytes_per_step": R * H * 4,
+           "call": "glmflash_moe_run_host (pinned host input / picks / weights in, output out, sync)"}
+    roofline = upstream = None
+    if G == 1:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+        peak, how = (float(peaks["bf16_tflops"]), "measured (MEASURED_PEAKS.json bf16_tflops, burst)") if peaks else (1590.0, "fallback")
+        # the dominant kernel alone: the gate/up grouped GEMM (2/3 of the flops)
+        fe = pkg.FastExperts(pkg.make_config(H, I, E, S, max_rows=R))
+        O = entry.load_oracle()
+        lay = []
+        for l in range(L):
+            ids, count, members = O.grouping(ps[l], R, S, E + 1, R)
+            t = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+            lay.append((t(ids), t(np.array([count], np.int32)), t(members)))
+
+        def fe_step():
+            l = state["i"] % L
+            state["i"] += 1
+            fe.run(structs[l], x_d[l], p_d[l], *lay[l], R, R)
+        timed(fe_step, L, 1)
+        fe.set_phases(4)
+        ms_gu = timed(fe_step, max(5, args.steps), 3)
+        fe.set_phases(8)
+        ms_dn = timed(fe_step, max(5, args.steps), 3)
+        fe.set_phases(15)
+        gu_flops = R * S * 2 * 2 * H * I
+        ach = gu_flops / (ms_gu * 1e-3) / 1e12
+        roofline = {"bound": "tensor", "kernel": "fast_gemm_kernel<2> (gate/up grouped GEMM: tcgen05 + in-kernel trellis decode + SwiGLU epilogue)",
+                    "achieved": ach, "peak": peak, "peak_source": how, "unit": "TFLOP/s", "frac": ach / peak, "ms_per_launch": ms_gu,
+                    "algorithmic_flops_per_launch": gu_flops, "traffic": None,
+                    "down_kernel": {"ms_per_launch": ms_dn, "tflops": R * S * 2 * H * I / (ms_dn * 1e-3) / 1e12},
+                    "layer": {"tflops": flops / (ms_step * 1e-3) / 1e12, "frac": flops / (ms_step * 1e-3) / 1e12 / peak}}
+        # the reference's own CUDA kernels, recompiled unmodified for sm_100a, on the same tensors (comparison only)
+        try:
+            sys.path.insert(0, os.path.join(ROOT, "oracle"))
+            import ref_gpu
+            if ref_gpu.available():
+                S6 = S + 1
+                l = 0
+                picks6 = torch.from_numpy(np.concatenate([ps[l], np.full((R, 1), E + 1, np.int32)], 1)).to(dev)
+
+                def up_step():
+                    ref_gpu.fast_experts_run(banks[l], x_d[l], picks6, *lay[l], R, R, H, I, E + 1, S6, stream=stream)
+                ms_up = timed(up_step, 3, 1)
+                upstream = {"what": "reference prefill kernels (mma.sync) compiled unmodified for sm_100a, experts only (no grouping/combine)",
+                            "ms_per_step": ms_up, "layer_tokens_per_s": R / (ms_up / 1e3), "tflops": flops / (ms_up * 1e-3) / 1e12}
+        except Exception as ex:
+            upstream = {"error": repr(ex)}
+    cpu = None
+    if rank == 0 and G == 1 and not args.no_cpu_baseline:
+        O = entry.load_oracle()
+        bank = synth.expert_bank(1000, H, I, E)
+        n = 32                                                     # a 32-token slice of the chunk, all host threads
+        t0 = time.time()
+        O.experts_run_rows(bank, H, I, E + 1, S, xs[0][:n], ps[0][:n], mode=0, sk_gu=4, sk_dn=1)
+        dt = time.time() - t0
+        cpu = {"value": n / dt, "unit": "layer-tokens/s", "cores": O.max_threads(), "kind": "port",
+               "sample": f"{n} of the {R} tokens of one chunk ({dt:.1f} s); every touched expert is unpacked once per slice"}
+    if rank == 0:
+        print(json.dumps({"metric": "EXL3-4bpw MoE layer tok/s", "value": R / (ms_step / 1e3), "unit": "layer-tokens/s", "n_gpus": G,
+                          "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
+                          "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
+                          "config": workload_config(args), "tflops": flops / (ms_step * 1e-3) / 1e12, "clocks": clocks, "e2e": e2e,
+                          "gpu_launches": 6 * args.steps, "roofline": roofline, "upstream_kernels_sm100a": upstream, "cpu_baseline": cpu}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def main():
@@ -164,9 +312,15 @@ def main():
     ap.add_argument("--rows", type=int, default=1)
     ap.add_argument("--layers", type=int, default=47)
     ap.add_argument("--impl", default="b200")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.workload == "prefill":
+        if args.rows == 1:
+            args.rows = 4096
+        if args.layers == 47:
+            args.layers = 2
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -188,6 +342,8 @@ def main():
     G = world
     R, L = args.rows, args.layers
     assert E % G == 0
+    if args.workload == "prefill":
+        return run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local)
 
     # ---- weights: one bank per layer, generated on the device (identical on every rank)
     banks = [synth.device_bank(1000 * l + 1, H, I, E, dev) for l in range(L)]

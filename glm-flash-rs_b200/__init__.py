@@ -58,6 +58,7 @@ SYMBOLS = {
     "glmflash_fast_experts_row_pairs": (_P, [_P]),
     "glmflash_fast_experts_plan": (_P, [_P]),
     "glmflash_fast_experts_status": (_P, [_P]),
+    "glmflash_fast_experts_set_phases": (_I, [_P, _I]),
     "glmflash_moe_new": (_I, [_P, _Z, _P]),
     "glmflash_moe_free": (None, [_P]),
     "glmflash_moe_run": (_I, [_P, _P, _P, _P, _I, _P, _P, _I]),
@@ -264,6 +265,9 @@ class FastExperts(_Owner):
         import torch
         return _view(lib().glmflash_fast_experts_xd(self._h), (self.cfg.max_rows * self.cfg.slots, self.cfg.inter),
                      torch.float16)
+
+    def set_phases(self, mask):
+        _check(lib().glmflash_fast_experts_set_phases(self._h, mask))
 
     @property
     def row_pairs(self):

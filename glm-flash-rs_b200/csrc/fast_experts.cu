@@ -531,6 +531,7 @@ struct glmflash_fast_experts {
     int *plan = nullptr, *src_pair = nullptr, *row_expert = nullptr, *status = nullptr;
     CUtensorMap map_xg, map_xu, map_xd;
     int sms = 0;
+    int phases = 15;                                        // profiling aid: 1 plan, 2 rotation, 4 gate/up, 8 down
 };
 
 extern "C" int glmflash_fast_experts_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_fast_experts **out) {
@@ -589,12 +590,14 @@ extern "C" int glmflash_fast_experts_run(glmflash_fast_experts *f, void *stream,
     cudaStream_t s = (cudaStream_t)stream;
     const int H = c.hidden, I = c.inter;
     const long P = (long)rows * c.slots;
-    fast_plan_kernel<<<1, FG_MAXU, 0, s>>>(ids, count, members, maxm, c.slots, c.experts, c.shared_exl3, c.expert_lo, c.expert_hi,
-                                          f->plan, f->src_pair, f->row_expert);
+    if (f->phases & 1)
+        fast_plan_kernel<<<1, FG_MAXU, 0, s>>>(ids, count, members, maxm, c.slots, c.experts, c.shared_exl3, c.expert_lo,
+                                              c.expert_hi, f->plan, f->src_pair, f->row_expert);
     GF_CUDA(cudaGetLastError());
     const int mats = shared_x ? 1 : 2;
     const long items = P * (H / 128) * mats;
-    fast_rot_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>((const __nv_bfloat16 *)input, x_stride, f->plan, f->src_pair,
+    if (f->phases & 2)
+        fast_rot_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>((const __nv_bfloat16 *)input, x_stride, f->plan, f->src_pair,
                                                               f->row_expert, (const __half *)w->suh_g, (const __half *)w->suh_u,
                                                               f->xg, f->xu, H, c.slots, mats);
     GF_CUDA(cudaGetLastError());
@@ -602,15 +605,20 @@ extern "C" int glmflash_fast_experts_run(glmflash_fast_experts *f, void *stream,
     a.ids = ids; a.plan = f->plan; a.src_pair = f->src_pair; a.status = f->status; a.limit = c.limit;
     a.T0 = w->gt; a.T1 = w->ut; a.sv0 = (const __half *)w->svh_g; a.sv1 = (const __half *)w->svh_u; a.sd = (const __half *)w->suh_d;
     a.xd = f->xd; a.y = nullptr; a.K = H; a.N = I; a.shared_x = shared_x ? 1 : 0;
-    fast_gemm_kernel<2><<<f->sms, FG_THREADS, FgCfg<2>::SMEM, s>>>(f->map_xg, f->map_xu, a);
+    if (f->phases & 4) fast_gemm_kernel<2><<<f->sms, FG_THREADS, FgCfg<2>::SMEM, s>>>(f->map_xg, f->map_xu, a);
     GF_CUDA(cudaGetLastError());
     a.T0 = w->dt; a.T1 = w->dt; a.sv0 = (const __half *)w->svh_d; a.sv1 = nullptr; a.sd = nullptr;
     a.xd = nullptr; a.y = f->out; a.K = I; a.N = H; a.shared_x = 1;
-    fast_gemm_kernel<1><<<f->sms, FG_THREADS, FgCfg<1>::SMEM, s>>>(f->map_xd, f->map_xd, a);
+    if (f->phases & 8) fast_gemm_kernel<1><<<f->sms, FG_THREADS, FgCfg<1>::SMEM, s>>>(f->map_xd, f->map_xd, a);
     GF_CUDA(cudaGetLastError());
     return 0;
 }
 
+extern "C" int glmflash_fast_experts_set_phases(glmflash_fast_experts *f, int mask) {
+    GF_REQUIRE(f != nullptr, "null argument");
+    f->phases = mask;
+    return 0;
+}
 extern "C" float *glmflash_fast_experts_output(const glmflash_fast_experts *f) { return f ? f->out : nullptr; }
 extern "C" const uint16_t *glmflash_fast_experts_xd(const glmflash_fast_experts *f) { return f ? (const uint16_t *)f->xd : nullptr; }
 extern "C" const int32_t *glmflash_fast_experts_row_pairs(const glmflash_fast_experts *f) { return f ? f->src_pair : nullptr; }

@@ -1,0 +1,82 @@
+"""Expert-parallel layer over 1/2/4/8 GPUs of one node (one process per GPU, torch.distributed for the plumbing).
+
+The reference shards every expert four ways by tensor parallelism and, after each MoE layer, all-gathers the
+ranks' fp32 partial outputs and adds them in fixed rank order (src/model.rs:485-496, src/comm.rs:1-2: "never sum
+in NCCL").  Here the shards are whole experts:
+  * routed expert e lives on rank e // (experts / world)              (contiguous windows)
+  * the shared expert (every row uses it) is owned by rank  layer % world   (round robin over the layers)
+  * grouping runs on every rank from the replicated picks (deterministic, so the ranks agree without talking)
+  * each rank computes the pairs of its window and combines them into a partial out_g[rows][hidden] fp32
+  * exchange = all-gather of the partials over NVLink (NCCL) + the same fixed rank-order sum as the reference
+The planning functions are pure python so that they are tested on CPU ranks (gloo) with the oracle as compute.
+"""
+
+
+def expert_window(rank, world, experts):
+    """[lo, hi) of routed expert ids computed on `rank`."""
+    if world < 1 or not 0 <= rank < world:
+        raise ValueError("rank outside the world")
+    if experts % world:
+        raise ValueError("the number of routed experts must be divisible by the world size")
+    per = experts // world
+    return rank * per, (rank + 1) * per
+
+
+def shared_owner(layer, world):
+    """Rank that computes the shared expert of `layer`."""
+    return layer % world
+
+
+def computed_here(picks, rank, world, experts, layer):
+    """Boolean mask [rows][slots]: which pairs this rank computes (the library's window rule)."""
+    import numpy as np
+    lo, hi = expert_window(rank, world, experts)
+    picks = np.asarray(picks)
+    routed = (picks >= lo) & (picks < hi) & (picks < experts)
+    shared = (picks >= experts) & (shared_owner(layer, world) == rank)
+    return routed | shared
+
+
+def exchange(partial, gathered, out, group=None, rank_sum=None):
+    """All-gather `partial` [rows][H] fp32 into `gathered` [world][rows][H] and add the ranks' rows in ascending
+    rank order into `out`.  `rank_sum(gathered, out)` is the device kernel (glmflash_rank_sum) on GPUs; on CPU
+    ranks the same ordered sum is done with torch."""
+    import torch.distributed as dist
+    dist.all_gather_into_tensor(gathered.view(-1), partial.reshape(-1), group=group)
+    if rank_sum is not None:
+        rank_sum(gathered, out)
+    else:
+        acc = gathered[0].clone()
+        for k in range(1, gathered.shape[0]):
+            acc += gathered[k]
+        out.copy_(acc)
+    return out
+
+
+class EpMoe:
+    """One MoE layer call, expert parallel: Moe handles with this rank's window (with and without the shared
+    expert), the exchange buffers, and run(layer, ...) -> final [rows][H] on every rank."""
+
+    def __init__(self, pkg, rank, world, max_rows, hidden=2048, inter=1536, experts=64, slots=5, group=None, device=None):
+        import torch
+        self.pkg, self.rank, self.world, self.group = pkg, rank, world, group
+        self.experts, self.hidden = experts, hidden
+        lo, hi = expert_window(rank, world, experts)
+        kinds = (1,) if world == 1 else (0, 1)
+        self.moes = {sh: pkg.Moe(pkg.make_config(hidden, inter, experts, slots, max_rows=max_rows, shared_exl3=sh,
+                                                 expert_lo=lo, expert_hi=hi)) for sh in kinds}
+        if world > 1:
+            self.gathered = torch.empty((world, max_rows, hidden), dtype=torch.float32, device=device)
+            self.final = torch.empty((max_rows, hidden), dtype=torch.float32, device=device)
+
+    def owner(self, layer):
+        return self.moes[1 if (self.world == 1 or shared_owner(layer, self.world) == self.rank) else 0]
+
+    def run(self, layer, w, x, picks, route_w, rows, out=None, stream=None):
+        m = self.owner(layer)
+        m.run(w, x, picks, route_w, rows, stream=stream)
+        if self.world == 1:
+            return m.output[:rows]
+        out = self.final[:rows] if out is None else out
+        g = self.gathered[:, :rows] if rows == self.gathered.shape[1] else self.gathered.view(-1)[: self.world * rows * self.hidden].view(self.world, rows, self.hidden)
+        return exchange(m.output[:rows], g, out, self.group, lambda a, b: self.pkg.rank_sum(a, b, stream=stream))

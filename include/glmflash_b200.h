@@ -149,6 +149,9 @@ const int32_t *glmflash_fast_experts_row_pairs(const glmflash_fast_experts *f);
 const int32_t *glmflash_fast_experts_plan(const glmflash_fast_experts *f);
 /* Device status word, as glmflash_experts_status. */
 const int32_t *glmflash_fast_experts_status(const glmflash_fast_experts *f);
+/* Profiling aid, as glmflash_experts_set_phases: 1 = plan, 2 = input rotation, 4 = gate/up GEMM, 8 = down GEMM
+ * (default 15). */
+int  glmflash_fast_experts_set_phases(glmflash_fast_experts *f, int mask);
 
 /* ---- Moe: the whole layer after routing  (src/moe.rs:11-182, src/batch.rs:1160-1210) ---------------- */
 typedef struct glmflash_moe glmflash_moe;

@@ -68,6 +68,7 @@ class Module:
 
 
 _mods = {}
+_fast_scratch = {}
 
 
 def module(name):
@@ -136,7 +137,7 @@ def grouping_run(picks, rows, max_rows):
     return ids, count, members
 
 
-def fast_experts_run(w, x, picks, ids, count, members, rows, maxm, H, I, E, slots, shared_x=False):
+def fast_experts_run(w, x, picks, ids, count, members, rows, maxm, H, I, E, slots, shared_x=False, stream=None):
     """Upstream FastExperts::run (src/fast_experts.rs:91-208).  Same trailing-slot convention as
     experts_run_rows.  Returns output fp32 [rows*slots][H], xd fp16 [rows*slots][I]."""
     import torch
@@ -145,29 +146,36 @@ def fast_experts_run(w, x, picks, ids, count, members, rows, maxm, H, I, E, slot
     dev = x.device
     P = rows * slots
     maxu = E + 1
-    xg = torch.zeros((P, H), dtype=torch.float16, device=dev)
-    xu = xg if shared_x else torch.zeros((P, H), dtype=torch.float16, device=dev)
-    xd = torch.zeros((P, I), dtype=torch.float16, device=dev)
-    out = torch.zeros((P, H), dtype=torch.float32, device=dev)
-    plan = torch.zeros(maxu + 3, dtype=torch.int32, device=dev)
+    key = (P, H, I, maxu, bool(shared_x), str(dev))
+    if stream is not None and key in _fast_scratch:           # timing mode: scratch is allocated once, as upstream's owner does
+        xg, xu, xd, out, plan = _fast_scratch[key]
+    else:
+        xg = torch.zeros((P, H), dtype=torch.float16, device=dev)
+        xu = xg if shared_x else torch.zeros((P, H), dtype=torch.float16, device=dev)
+        xd = torch.zeros((P, I), dtype=torch.float16, device=dev)
+        out = torch.zeros((P, H), dtype=torch.float32, device=dev)
+        plan = torch.zeros(maxu + 3, dtype=torch.int32, device=dev)
+        if stream is not None:
+            torch.cuda.synchronize()
+            _fast_scratch[key] = (xg, xu, xd, out, plan)
     sms = torch.cuda.get_device_properties(dev).multi_processor_count
     p = lambda t: t.data_ptr()
     if shared_x:
         items = P * (H // 128)
-        pf.launch("fast_rot_in", ((items + 7) // 8, 1, 1), 256, [p(x), x.stride(0), p(picks), p(w["suh_g"]), p(xg), H, slots, items])
+        pf.launch("fast_rot_in", ((items + 7) // 8, 1, 1), 256, [p(x), x.stride(0), p(picks), p(w["suh_g"]), p(xg), H, slots, items], stream=stream)
     else:
         base.launch("rot_in_kernel", (P, H // 128, 2), 32,
-                    [p(x), x.stride(0), p(picks), p(w["suh_g"]), p(w["suh_u"]), p(xg), p(xu), H, slots])
+                    [p(x), x.stride(0), p(picks), p(w["suh_g"]), p(w["suh_u"]), p(xg), p(xu), H, slots], stream=stream)
     ticket = p(plan) + (maxu + 2) * 4
-    pf.launch("fast_expert_plan", (1, 1, 1), 1024, [p(ids), p(count), p(members), maxu, maxm, E, 64, p(plan)])
+    pf.launch("fast_expert_plan", (1, 1, 1), 1024, [p(ids), p(count), p(members), maxu, maxm, E, 64, p(plan)], stream=stream)
     gu, smem, occ = ("fast_gu_shared", 49152, 2) if shared_x else ("fast_gu_separate", 73728, 1)
     pf.launch(gu, (sms * occ, 1, 1), 256,
               [p(xg), p(xu), p(w["gt"]), p(w["ut"]), p(ids), p(members), p(plan), ticket, H, I, maxm, slots, maxu,
-               p(w["svh_g"]), p(w["svh_u"]), p(w["suh_d"]), p(xd), 0, 10.0], smem=smem)
+               p(w["svh_g"]), p(w["svh_u"]), p(w["suh_d"]), p(xd), 0, 10.0], smem=smem, stream=stream)
     large = maxm >= 4096
-    pf.launch("fast_expert_plan", (1, 1, 1), 1024, [p(ids), p(count), p(members), maxu, maxm, E, 128 if large else 64, p(plan)])
+    pf.launch("fast_expert_plan", (1, 1, 1), 1024, [p(ids), p(count), p(members), maxu, maxm, E, 128 if large else 64, p(plan)], stream=stream)
     dn, smem = ("fast_down_large", 33792) if large else ("fast_down", 36864)
     pf.launch(dn, (sms * 2, 1, 1), 128,
               [p(xd), p(xd), p(w["dt"]), p(w["dt"]), p(ids), p(members), p(plan), ticket, I, H, maxm, slots, maxu,
-               p(w["svh_d"]), p(w["svh_d"]), p(w["svh_d"]), 0, p(out), 0.0], smem=smem)
+               p(w["svh_d"]), p(w["svh_d"]), p(w["svh_d"]), 0, p(out), 0.0], smem=smem, stream=stream)
     return out, xd

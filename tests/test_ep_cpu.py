@@ -1,0 +1,87 @@
+"""Expert-parallel planning and exchange on CPU ranks (gloo, world size 2 and 4): every pair is computed on exactly
+one rank, and the rank-ordered sum of the ranks' partial layer outputs equals the single-rank combine.  The oracle
+stands in for the GPU kernels (this is host logic; the GPU path is tested under -m gpu)."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, rel_err
+
+H, I, E, S, R, LAYERS = 256, 256, 4, 3, 5, 3
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    entry.load_package()
+    from glmflash_b200 import ep, synth
+    O = entry.load_oracle()
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        worst = 0.0
+        for layer in range(LAYERS):
+            bank = synth.expert_bank(50 + layer, H, I, E, svh_scale=True)
+            x = synth.activations_bf16(60 + layer, R, H)
+            picks, rw = synth.route(70 + layer, R, E, S - 1)
+            Y = O.experts_run_rows(bank, H, I, E + 1, S, x, picks, mode=1, threads=1)
+            full = O.combine(Y, rw, R, S, H)
+            mine = ep.computed_here(picks, rank, world, E, layer)
+            wmask = np.where(mine, np.concatenate([rw[:, :-1], np.ones((R, 1), np.float32)], 1), 0).astype(np.float32)
+            # partial combine of this rank: masked pairs contribute nothing (their Y rows are never computed on a GPU rank)
+            Ym = np.where(np.repeat(mine.reshape(-1, 1), H, 1), Y, 0).astype(np.float32)
+            part = (wmask.reshape(R, S, 1) * Ym.reshape(R, S, H)).sum(1).astype(np.float32)
+            gathered = torch.empty((world, R, H), dtype=torch.float32)
+            out = torch.empty((R, H), dtype=torch.float32)
+            ep.exchange(torch.from_numpy(part), gathered, out)
+            # every rank holds the same bytes, and they are the single-rank result up to fp32 re-association
+            chk = [torch.empty_like(out) for _ in range(world)]
+            dist.all_gather(chk, out)
+            assert all(torch.equal(chk[0], c) for c in chk)
+            worst = max(worst, rel_err(out.numpy(), full)[0])
+            owners = torch.zeros((R, S), dtype=torch.int32) + torch.from_numpy(mine.astype(np.int32))
+            dist.all_reduce(owners)
+            assert (owners == 1).all(), "a pair must be computed on exactly one rank"
+        q.put((rank, worst))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_ep_exchange_gloo(world):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+        assert p.exitcode == 0
+    res = [q.get(timeout=5) for _ in range(world)]
+    assert sorted(r for r, _ in res) == list(range(world))
+    assert max(w for _, w in res) < 1e-5
+
+
+def test_windows(pkg):
+    from glmflash_b200 import ep
+    for world in (1, 2, 4, 8):
+        wins = [ep.expert_window(r, world, 64) for r in range(world)]
+        assert wins[0][0] == 0 and wins[-1][1] == 64 and all(a[1] == b[0] for a, b in zip(wins, wins[1:]))
+        assert sorted(ep.shared_owner(l, world) for l in range(world)) == list(range(world))
+    with pytest.raises(ValueError):
+        ep.expert_window(0, 3, 64)
+    with pytest.raises(ValueError):
+        ep.expert_window(2, 2, 64)
