@@ -59,7 +59,7 @@ class ClockSampler:
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "25",
                                           "-i", str(self.idx)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=lambda: self.lines.extend(self.proc.stdout), daemon=True)
             self.t.start()
@@ -218,7 +218,6 @@ def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
     if rank == 0:
         sampler.start()
     ms_step = timed(step, args.steps, args.warmup)
-    clocks = sampler.stop() if rank == 0 else None
     flops = R * S * 3 * 2 * H * I                                  # all pairs incl. the shared expert, three matrices
     xh = torch.from_numpy(xs.view(np.int16)).pin_memory()
     ph, wh = torch.from_numpy(ps).pin_memory(), torch.from_numpy(ws).pin_memory()
@@ -284,6 +283,7 @@ def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
                             "ms_per_step": ms_up, "layer_tokens_per_s": R / (ms_up / 1e3), "tflops": flops / (ms_up * 1e-3) / 1e12}
         except Exception as ex:
             upstream = {"error": repr(ex)}
+    clocks = sampler.stop() if rank == 0 else None       # sampled over every timed region above
     cpu = None
     if rank == 0 and G == 1 and not args.no_cpu_baseline:
         O = entry.load_oracle()
@@ -300,8 +300,20 @@ def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
                           "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
                           "config": workload_config(args), "tflops": flops / (ms_step * 1e-3) / 1e12, "clocks": clocks, "e2e": e2e,
                           "gpu_launches": 6 * args.steps, "roofline": roofline, "upstream_kernels_sm100a": upstream, "cpu_baseline": cpu}))
+    finish(world, dist)
+
+
+def finish(world, dist):
+    """Leave without tearing the process group down (destroy_process_group can block after graph-captured
+    collectives); every rank has passed the final barrier of its last timed region by now."""
+    sys.stdout.flush()
+    sys.stderr.flush()
     if world > 1:
-        dist.destroy_process_group()
+        try:
+            dist.barrier()
+        except Exception:
+            pass
+        os._exit(0)
 
 
 def main():
@@ -417,7 +429,6 @@ def main():
     if rank == 0:
         sampler.start()
     ms_step = timed(step, args.steps, args.warmup)
-    clocks = sampler.stop() if rank == 0 else None
     value = R * L / (ms_step / 1e3)
 
     # ---- end to end: pinned host buffers through the host-buffer C-ABI call, every layer, every step
@@ -471,6 +482,7 @@ def main():
                               "gbs": (float(np.mean(distinct)) * W_E + R * H * 6) / (ms_step / L * 1e-3) / 1e9}}
         roofline["layer"]["frac"] = roofline["layer"]["gbs"] / peak
 
+    clocks = sampler.stop() if rank == 0 else None       # sampled over every timed region above
     cpu = None
     if rank == 0 and G == 1 and not args.no_cpu_baseline:
         O = entry.load_oracle()
@@ -485,8 +497,7 @@ def main():
                "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * L * args.steps + (0 if G == 1 else L * args.steps),
                "roofline": roofline, "cpu_baseline": cpu}
         print(json.dumps(out))
-    if world > 1:
-        dist.destroy_process_group()
+    finish(world, dist)
 
 
 if __name__ == "__main__":

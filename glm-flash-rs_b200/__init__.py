@@ -16,7 +16,7 @@ SO_PATH = os.path.join(_HERE, "libglmflash_b200.so")
 class Config(C.Structure):
     _fields_ = [("hidden", C.c_int32), ("inter", C.c_int32), ("experts", C.c_int32), ("slots", C.c_int32),
                 ("max_rows", C.c_int32), ("shared_exl3", C.c_int32), ("expert_lo", C.c_int32),
-                ("expert_hi", C.c_int32), ("limit", C.c_float), ("reserved", C.c_int32 * 7)]
+                ("expert_hi", C.c_int32), ("limit", C.c_float), ("pdl", C.c_int32), ("reserved", C.c_int32 * 6)]
 
 
 class Weights(C.Structure):
@@ -98,9 +98,9 @@ def _check(rc):
 
 
 def make_config(hidden=2048, inter=1536, experts=64, slots=5, max_rows=1, shared_exl3=1, expert_lo=0,
-                expert_hi=None, limit=10.0):
+                expert_hi=None, limit=10.0, pdl=1):
     return Config(hidden, inter, experts, slots, max_rows, shared_exl3, expert_lo,
-                  experts if expert_hi is None else expert_hi, limit)
+                  experts if expert_hi is None else expert_hi, limit, pdl)
 
 
 def _torch():

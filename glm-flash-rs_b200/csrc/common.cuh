@@ -31,6 +31,24 @@ int fail_cuda(cudaError_t e, const char *what);
         if (!(cond)) return gf::fail(msg);   \
     } while (0)
 
+// Launch with or without the programmatic-dependent-launch attribute (the kernel's griddepcontrol instructions
+// are no-ops without it).
+template <typename... KArgs, typename... Args>
+int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = pdl ? at : nullptr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    GF_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    return 0;
+}
+
 // ---- codebook ------------------------------------------------------------------------------------------
 // The 32-bit codeword of a 16-bit trellis state: two fp16 halves whose sum is the weight
 // (upstream native/exl3.cu:21-25).

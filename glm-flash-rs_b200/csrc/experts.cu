@@ -14,20 +14,17 @@ static int set_smem(F *kernel, size_t bytes) {
 
 int launch_rot_in(cudaStream_t s, const void *x, bool x_is_bf16, int x_stride, const int *picks, const __half *suh0,
                   const __half *suh1, __half *out0, __half *out1, int K, int slots, int P, int mats, int E,
-                  int shared_exl3, int e_lo, int e_hi) {
+                  int shared_exl3, int e_lo, int e_hi, bool pdl) {
     const long items = (long)P * (K / 128) * mats;
     const unsigned grid = (unsigned)((items + 7) / 8);
     if (x_is_bf16)
-        rot_in_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16 *)x, x_stride, picks, suh0, suh1, out0,
-                                                          out1, K, slots, P, mats, E, shared_exl3, e_lo, e_hi);
-    else
-        rot_in_kernel<__half><<<grid, 256, 0, s>>>((const __half *)x, x_stride, picks, suh0, suh1, out0, out1, K, slots,
-                                                    P, mats, E, shared_exl3, e_lo, e_hi);
-    GF_CUDA(cudaGetLastError());
-    return 0;
+        return launch_k(rot_in_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, pdl, (const __nv_bfloat16 *)x, x_stride,
+                        picks, suh0, suh1, out0, out1, K, slots, P, mats, E, shared_exl3, e_lo, e_hi);
+    return launch_k(rot_in_kernel<__half>, dim3(grid), dim3(256), 0, s, pdl, (const __half *)x, x_stride, picks, suh0, suh1,
+                    out0, out1, K, slots, P, mats, E, shared_exl3, e_lo, e_hi);
 }
 
-int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax) {
+int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax, bool pdl) {
     const int sets = a.maxm > 8 ? 2 : 1;
     const size_t smem = gemv_smem_bytes(mats, sets);
     static bool configured_dev[64] = {};
@@ -42,12 +39,11 @@ int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax) {
         configured = true;
     }
     const dim3 grid((unsigned)(a.N / 128), (unsigned)a.SK, (unsigned)umax);
-    if (mats == 2 && sets == 1) gemv_kernel<2, 1><<<grid, GEMV_THREADS, smem, s>>>(a);
-    else if (mats == 2) gemv_kernel<2, 2><<<grid, GEMV_THREADS, smem, s>>>(a);
-    else if (sets == 1) gemv_kernel<1, 1><<<grid, GEMV_THREADS, smem, s>>>(a);
-    else gemv_kernel<1, 2><<<grid, GEMV_THREADS, smem, s>>>(a);
-    GF_CUDA(cudaGetLastError());
-    return 0;
+    const dim3 block(GEMV_THREADS);
+    if (mats == 2 && sets == 1) return launch_k(gemv_kernel<2, 1>, grid, block, smem, s, pdl, a);
+    if (mats == 2) return launch_k(gemv_kernel<2, 2>, grid, block, smem, s, pdl, a);
+    if (sets == 1) return launch_k(gemv_kernel<1, 1>, grid, block, smem, s, pdl, a);
+    return launch_k(gemv_kernel<1, 2>, grid, block, smem, s, pdl, a);
 }
 
 int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit) {
@@ -123,11 +119,12 @@ extern "C" int glmflash_experts_run_rows(glmflash_experts *e, void *stream, cons
     GF_REQUIRE(((uintptr_t)w->gt | (uintptr_t)w->ut | (uintptr_t)w->dt) % 16 == 0, "trellis tensors must be 16-byte aligned");
     GF_REQUIRE(((uintptr_t)input) % 8 == 0, "input must be 8-byte aligned");
     cudaStream_t s = (cudaStream_t)stream;
+    const bool pdl = c.pdl != 0;
     const int H = c.hidden, I = c.inter, P = rows * c.slots, E1 = c.experts + 1;
     const int umax = std::min(rows * (c.slots - 1) + 1, E1);
     if ((e->phases & 1) &&
         launch_rot_in(s, input, true, x_stride, picks, (const __half *)w->suh_g, (const __half *)w->suh_u, e->xg, e->xu, H,
-                      c.slots, P, 2, c.experts, c.shared_exl3, c.expert_lo, c.expert_hi))
+                      c.slots, P, 2, c.experts, c.shared_exl3, c.expert_lo, c.expert_hi, pdl))
         return -1;
     GemvArgs a{};
     a.ids = ids; a.count = count; a.members = members;
@@ -138,13 +135,13 @@ extern "C" int glmflash_experts_run_rows(glmflash_experts *e, void *stream, cons
     a.X0 = e->xg; a.X1 = e->xu; a.T0 = w->gt; a.T1 = w->ut;
     a.sv0 = (const __half *)w->svh_g; a.sv1 = (const __half *)w->svh_u; a.sd = (const __half *)w->suh_d;
     a.xd = e->xd; a.y = nullptr; a.K = H; a.N = I; a.SK = e->sk_gu; a.mode = GEMV_GATEUP;
-    if ((e->phases & 2) && launch_gemv(s, 2, a, umax)) return -1;
+    if ((e->phases & 2) && launch_gemv(s, 2, a, umax, pdl)) return -1;
     if (!(e->phases & 4)) return 0;
     // down -> y
     a.X0 = e->xd; a.X1 = e->xd; a.T0 = w->dt; a.T1 = w->dt;
     a.sv0 = (const __half *)w->svh_d; a.sv1 = nullptr; a.sd = nullptr;
     a.xd = nullptr; a.y = e->y; a.K = I; a.N = H; a.SK = e->sk_dn; a.mode = GEMV_DOWN;
-    return launch_gemv(s, 1, a, umax);
+    return launch_gemv(s, 1, a, umax, pdl);
 }
 
 extern "C" int glmflash_experts_set_phases(glmflash_experts *e, int mask) {
@@ -167,7 +164,7 @@ LinearScratch linear_layout(int K, int N) {
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) / 256 * 256; return o; };
     L.xr = take((size_t)16 * K * 2);
-    L.z = take((size_t)(K / GEMV_KC) * 16 * N * 4);
+    L.z = take((size_t)(K / GEMV_KC) * 16 * N * 4);   // [SK][16 rows][N]
     L.tickets = take((size_t)(N / 128) * 4);
     L.tables = take((size_t)(2 + 16) * 4 + 4);      // ids[1], count[1], members[16], status
     L.total = off;
@@ -200,7 +197,7 @@ extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, c
     linear_tables_kernel<<<1, 32, 0, s>>>(tables, rows);
     GF_CUDA(cudaGetLastError());
     __half *xr = (__half *)(base + L.xr);
-    if (launch_rot_in(s, x, false, K, nullptr, (const __half *)suh, (const __half *)suh, xr, xr, K, 1, rows, 1, 1, 1, 0, 2))
+    if (launch_rot_in(s, x, false, K, nullptr, (const __half *)suh, (const __half *)suh, xr, xr, K, 1, rows, 1, 1, 1, 0, 2, false))
         return -1;
     GemvArgs a{};
     a.X0 = xr; a.X1 = xr; a.T0 = words; a.T1 = words;
@@ -209,7 +206,7 @@ extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, c
     a.sv0 = (const __half *)svh; a.xd = (__half *)y;
     a.K = K; a.N = N; a.P = rows; a.SK = K / GEMV_KC; a.maxm = rows; a.slots = 1; a.E = 1; a.e_lo = 0; a.e_hi = 1;
     a.shared_exl3 = 1; a.mode = GEMV_LINEAR; a.limit = 10.f;
-    return launch_gemv(s, 1, a, 1);
+    return launch_gemv(s, 1, a, 1, false);
 }
 
 // ---- the single EXL3 linear for callers that must not allocate ------------------------------------------------
@@ -220,7 +217,7 @@ extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, c
 // The array is part of every loaded copy of the library: each GPU that loads it holds these bytes until exit.
 namespace {
 constexpr int STATIC_LINEAR_MAX_K = 2048, STATIC_LINEAR_MAX_N = 2048;
-constexpr size_t STATIC_LINEAR_BYTES = 1179648;           // 1.125 MiB >= linear_layout(2048, 2048).total
+constexpr size_t STATIC_LINEAR_BYTES = 2228224;           // 2.125 MiB >= linear_layout(2048, 2048).total
 static __device__ __align__(256) unsigned char g_static_linear_scratch[STATIC_LINEAR_BYTES];
 void *g_static_linear_ptr[64] = {};                       // device address of the array, per device ordinal
 }  // namespace

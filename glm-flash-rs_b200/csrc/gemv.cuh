@@ -4,8 +4,8 @@
 // (native/exl3.cu:59-170,260-321, native/expert_loads.cu:130-285).  Same operands and the same member /
 // pair conventions; a different machine mapping:
 //
-//   * work item = (distinct expert u, 128-column block nb, K split): MATS matrices x 16 k-tiles x 8 n-tiles,
-//     i.e. MATS x 16 contiguous 1-KB rows of packed trellis words.  One elected warp issues them all as TMA
+//   * work item = (distinct expert u, 128-column block nb, K split): MATS matrices x 8 k-tiles x 8 n-tiles,
+//     i.e. MATS x 8 contiguous 1-KB rows of packed trellis words.  One elected warp issues them all as TMA
 //     bulk copies (cp.async.bulk) into shared memory at kernel start, four k-tiles per mbarrier, so the whole
 //     item is in flight before anything else happens and the copy engine, not the warps, follows the stream.
 //   * a lane reads 16 bytes (4 words of one tile) with one LDS.128: that is 32 weights, all 16 k of two
@@ -29,9 +29,10 @@
 
 namespace gf {
 
-constexpr int GEMV_THREADS = 256;
-constexpr int GEMV_KTC = 16;                       // k-tiles per CTA item (per matrix)
-constexpr int GEMV_KC = GEMV_KTC * 16;             // 256 k per CTA item
+constexpr int GEMV_THREADS = 128;
+constexpr int GEMV_KTC = 8;                        // k-tiles per CTA item (per matrix)
+constexpr int GEMV_KC = GEMV_KTC * 16;             // 128 k per CTA item
+constexpr int GEMV_GROUPS = GEMV_KTC / 4;          // mbarriers (4 k-tiles each)
 constexpr int GEMV_WROW = 1024 + 32;               // bytes per staged weight row (1 KB + 32 B: conflict-free LDS.128)
 constexpr int GEMV_AST = GEMV_KC + 8;              // dwords per staged activation row (+32 B pad)
 constexpr int GEMV_PST = 132;                      // floats per partial row
@@ -67,18 +68,20 @@ __device__ __forceinline__ uint32_t weight_dup(uint32_t x) {
 // dynamic shared memory size of a launch
 inline size_t gemv_smem_bytes(int mats, int sets) {
     size_t w = (size_t)mats * GEMV_KTC * GEMV_WROW;
-    size_t part = (size_t)2 * 16 * GEMV_PST * sizeof(float);
+    size_t part = (size_t)2 * sets * 8 * GEMV_PST * sizeof(float);
     size_t a = (size_t)mats * sets * 8 * GEMV_AST * 4;
     return 64 + (w > part ? w : part) + a;
 }
 
+// Work item (CTA) = (distinct expert u, 128-column block nb, K split of 128): MATS x 8 rows of 1 KB.
+// 4 warps.  MATS = 2: warp = (matrix, half of the 8 n-tiles), both 4-k-tile groups.  MATS = 1: warp = (group, half).
 template <int MATS, int SETS>
-__global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 8 : 5) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                         // 4 barriers (one per 4 k-tiles)
-    unsigned char *wsm = smem + 64;                                              // [MATS][16] rows of GEMV_WROW
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                         // one barrier per 4 k-tiles
+    unsigned char *wsm = smem + 64;                                              // [MATS][8] rows of GEMV_WROW
     constexpr size_t WBYTES = (size_t)MATS * GEMV_KTC * GEMV_WROW;
-    constexpr size_t PBYTES = (size_t)2 * 16 * GEMV_PST * sizeof(float);
+    constexpr size_t PBYTES = (size_t)2 * SETS * 8 * GEMV_PST * sizeof(float);
     constexpr size_t WP = WBYTES > PBYTES ? WBYTES : PBYTES;
     float *part = reinterpret_cast<float *>(wsm);                                // aliases wsm after the K loop
     uint32_t *asm_ = reinterpret_cast<uint32_t *>(wsm + WP);                     // [MATS][SETS*8][GEMV_AST]
@@ -90,14 +93,18 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     const int nb = blockIdx.x, split = blockIdx.y, u = blockIdx.z;
     const int KT = a.K >> 4, NTILES = a.N >> 4, NB = a.N >> 7;
 
-    if (tid == 0) {
-#pragma unroll
-        for (int g = 0; g < 4; ++g) mbar_init(bars + g, 1);
-        mbar_fence_init();
-    }
+    // one round trip for everything the prologue needs (none of the three loads depends on another)
     const int cnt = __ldcg(a.count);
     const int e = __ldcg(a.ids + u);
+    int code = -1;
+    if (tid < 16 && tid < a.maxm) code = __ldcg(a.members + (size_t)u * a.maxm + tid);
+    if (tid == 0) {
+#pragma unroll
+        for (int g = 0; g < GEMV_GROUPS; ++g) mbar_init(bars + g, 1);
+        mbar_fence_init();
+    }
     if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the CTA
+    if (tid < 16) rows_sh[tid] = code >= 0 ? (code >> 5) * a.slots + (code & 31) : -1;
     __syncthreads();
 
     // ---- the whole item's packed words, in flight at once
@@ -105,28 +112,21 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     if (warp == 0) {
         if (lane == 0) {
 #pragma unroll
-            for (int g = 0; g < 4; ++g) mbar_expect_tx(bars + g, MATS * 4 * 1024);
+            for (int g = 0; g < GEMV_GROUPS; ++g) mbar_expect_tx(bars + g, MATS * 4 * 1024);
         }
         __syncwarp();
-        for (int r = lane; r < MATS * GEMV_KTC; r += 32) {
-            const int mat = r / GEMV_KTC, ktl = r % GEMV_KTC;
+        if (lane < MATS * GEMV_KTC) {
+            const int mat = lane / GEMV_KTC, ktl = lane % GEMV_KTC;
             const uint32_t *T_ = mat ? a.T1 : a.T0;
             const uint32_t *src = T_ + (((size_t)e * KT + kt0 + ktl) * NTILES + (size_t)nb * 8) * 32;
-            tma_load_1d(wsm + (size_t)r * GEMV_WROW, src, 1024, bars + (ktl >> 2));
+            tma_load_1d(wsm + (size_t)lane * GEMV_WROW, src, 1024, bars + (ktl >> 2));
         }
     }
     pdl_launch_dependents();
-
-    // ---- members of this expert: pair rows
-    if (tid < 16) {
-        const int code = tid < a.maxm ? __ldcg(a.members + (size_t)u * a.maxm + tid) : -1;
-        rows_sh[tid] = code >= 0 ? (code >> 5) * a.slots + (code & 31) : -1;
-    }
-    pdl_wait();                                   // X / Z / tickets belong to the kernels before this one
-    __syncthreads();
     int nmem = 0;
 #pragma unroll
-    for (int m = 0; m < 16; ++m) nmem += rows_sh[m] >= 0;   // members come first
+    for (int m = 0; m < SETS * 8; ++m) nmem += rows_sh[m] >= 0;   // members come first
+    pdl_wait();                                   // X / Z / tickets belong to the kernels before this one
 
     // ---- stage the members' activations of this K range as (x_k, 0) pairs, permuted to the mma order:
     //      dword position of local k = 64 g + 16 T + 8 h + 2 t + b  is  g*64 + (2t + h)*8 + 2T + b.
@@ -135,9 +135,9 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     {
         const int k0 = kt0 * 16;
         const int items = MATS * nmem * (GEMV_KC / 2);
-#pragma unroll 4
         for (int i = tid; i < items; i += GEMV_THREADS) {
-            const int kp = i % (GEMV_KC / 2), m = (i / (GEMV_KC / 2)) % nmem, mat = i / ((GEMV_KC / 2) * nmem);
+            const int kp = i % (GEMV_KC / 2), mm = i / (GEMV_KC / 2);
+            const int m = mm % nmem, mat = mm / nmem;
             const int p = rows_sh[m];
             const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>((mat ? a.X1 : a.X0) + (size_t)p * a.K + k0) + kp);
             const int kl = 2 * kp;
@@ -149,22 +149,22 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
     }
     __syncthreads();
 
-    // ---- K loop.  MATS = 2: warp = (matrix, n-tile pair), all 4 groups.  MATS = 1: warp = (K half, pair).
-    const int sub = warp >> 2, ntp = warp & 3;
+    // ---- K loop
+    const int sub = warp >> 1, nth = warp & 1;
     const int mat = MATS == 2 ? sub : 0;
-    const int g_begin = MATS == 2 ? 0 : sub * 2, g_end = MATS == 2 ? 4 : sub * 2 + 2;
+    const int g_begin = MATS == 2 ? 0 : sub, g_end = MATS == 2 ? GEMV_GROUPS : sub + 1;
     const bool two_sets = SETS == 2 && nmem > 8;
-    float acc[2][SETS][4];
+    float acc[4][SETS][4];
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
+    for (int n = 0; n < 4; ++n)
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[n][s][c] = 0.f;
 
     bool ok = true;
+#pragma unroll 1
     for (int g = g_begin; g < g_end; ++g) {
-        if (!mbar_wait(bars + g, 0)) { ok = false; break; }
         // B operands of the group's 8 mma: (x, 0) pairs of member G (set 0) and member 8 + G (set 1)
         uint2 b[SETS][8];
 #pragma unroll
@@ -173,10 +173,11 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
 #pragma unroll
             for (int m = 0; m < 8; ++m) b[s][m] = *reinterpret_cast<const uint2 *>(ar + m * 8);
         }
+        if (!mbar_wait(bars + g, 0)) { ok = false; break; }
+        const unsigned char *wrow = wsm + ((size_t)mat * GEMV_KTC + 4 * g + T) * GEMV_WROW + nth * 512 + G * 16;
 #pragma unroll
-        for (int n = 0; n < 2; ++n) {
-            const uint4 wv = *reinterpret_cast<const uint4 *>(wsm + ((size_t)mat * GEMV_KTC + 4 * g + T) * GEMV_WROW +
-                                                               (ntp * 2 + n) * 128 + G * 16);
+        for (int n = 0; n < 4; ++n) {
+            const uint4 wv = *reinterpret_cast<const uint4 *>(wrow + n * 128);
             const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
             const uint32_t before = __shfl_sync(0xffffffffu, wv.w, (lane + 28) & 31);   // word 4G-1 (circular)
 #pragma unroll
@@ -205,23 +206,23 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
 
     // ---- partial[sub][member][column]
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
+    for (int n = 0; n < 4; ++n)
 #pragma unroll
         for (int s = 0; s < SETS; ++s) {
-            const int col = (ntp * 2 + n) * 16 + G, mem = s * 8 + 2 * T;
-            float *pp = part + ((size_t)sub * 16 + mem) * GEMV_PST + col;
+            const int col = (nth * 4 + n) * 16 + G, mem = s * 8 + 2 * T;
+            float *pp = part + ((size_t)sub * SETS * 8 + mem) * GEMV_PST + col;
             pp[0] = acc[n][s][0];
             pp[GEMV_PST] = acc[n][s][1];
             pp[8] = acc[n][s][2];
             pp[GEMV_PST + 8] = acc[n][s][3];
         }
     __syncthreads();
-    for (int i = tid; i < MATS * 16 * 32; i += GEMV_THREADS) {
-        const int c4 = i & 31, m = (i >> 5) & 15, mt = i >> 9;
-        if (m >= nmem || (SETS == 1 && m >= 8)) continue;
-        float4 v = *reinterpret_cast<const float4 *>(part + ((size_t)mt * 16 + m) * GEMV_PST + 4 * c4);
+    for (int i = tid; i < MATS * nmem * 32; i += GEMV_THREADS) {
+        const int c4 = i & 31, mm = i >> 5;
+        const int m = mm % nmem, mt = mm / nmem;
+        float4 v = *reinterpret_cast<const float4 *>(part + ((size_t)mt * SETS * 8 + m) * GEMV_PST + 4 * c4);
         if (MATS == 1) {
-            const float4 w2 = *reinterpret_cast<const float4 *>(part + ((size_t)16 + m) * GEMV_PST + 4 * c4);
+            const float4 w2 = *reinterpret_cast<const float4 *>(part + ((size_t)SETS * 8 + m) * GEMV_PST + 4 * c4);
             v.x += w2.x; v.y += w2.y; v.z += w2.z; v.w += w2.w;
         }
         float *z = a.Z + (((size_t)mt * a.SK + split) * a.P + rows_sh[m]) * a.N + nb * 128 + 4 * c4;
@@ -246,11 +247,14 @@ __global__ void __launch_bounds__(GEMV_THREADS) gemv_kernel(const GemvArgs a) {
         const int p = rows_sh[m];
         const int n0 = nb * 128 + 4 * lane;
         float v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
+        const float *z0 = a.Z + (size_t)p * a.N + n0;
+        const size_t zs = (size_t)a.P * a.N;
+#pragma unroll 4
         for (int s = 0; s < a.SK; ++s) {
-            const float4 q = __ldcg(reinterpret_cast<const float4 *>(a.Z + (((size_t)s) * a.P + p) * a.N + n0));
+            const float4 q = __ldcg(reinterpret_cast<const float4 *>(z0 + s * zs));
             v0[0] += q.x; v0[1] += q.y; v0[2] += q.z; v0[3] += q.w;
             if (MATS == 2) {
-                const float4 r = __ldcg(reinterpret_cast<const float4 *>(a.Z + (((size_t)a.SK + s) * a.P + p) * a.N + n0));
+                const float4 r = __ldcg(reinterpret_cast<const float4 *>(z0 + (a.SK + s) * zs));
                 v1[0] += r.x; v1[1] += r.y; v1[2] += r.z; v1[3] += r.w;
             }
         }
@@ -299,6 +303,9 @@ __global__ void __launch_bounds__(256) rot_in_kernel(const IN *__restrict__ x, i
                                                      const __half *__restrict__ suh0, const __half *__restrict__ suh1,
                                                      __half *__restrict__ out0, __half *__restrict__ out1, int K, int slots,
                                                      int P, int mats, int E, int shared_exl3, int e_lo, int e_hi) {
+    // Wait first, trigger second: the kernel after this one reads the grouping tables in its prologue, before its own
+    // wait, so it may only start once everything before this kernel (the grouping, the producer of x) has completed.
+    pdl_wait();
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = K >> 7;
@@ -312,7 +319,6 @@ __global__ void __launch_bounds__(256) rot_in_kernel(const IN *__restrict__ x, i
         e = picks[p];
         if (expert_skipped(e, E, shared_exl3, e_lo, e_hi)) return;
     }
-    pdl_wait();
     const __half *suh = (mat ? suh1 : suh0) + (size_t)e * K + blk * 128 + 4 * lane;
     const IN *xr = x + (size_t)row * x_stride + blk * 128 + 4 * lane;
     float v[4];
@@ -328,7 +334,7 @@ __global__ void __launch_bounds__(256) rot_in_kernel(const IN *__restrict__ x, i
 // Host-side launch helpers (defined in experts.cu).
 int launch_rot_in(cudaStream_t s, const void *x, bool x_is_bf16, int x_stride, const int *picks, const __half *suh0,
                   const __half *suh1, __half *out0, __half *out1, int K, int slots, int P, int mats, int E,
-                  int shared_exl3, int e_lo, int e_hi);
-int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax);
+                  int shared_exl3, int e_lo, int e_hi, bool pdl);
+int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax, bool pdl);
 
 }  // namespace gf

@@ -27,8 +27,8 @@ __global__ void __launch_bounds__(GROUP_THREADS) grouping_kernel(const int *__re
     __shared__ int warp_sums[32];
     __shared__ int base_sh;
     const int e = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();                                   // picks may be the previous kernel's output; ids / members its input
     pdl_launch_dependents();
-    pdl_wait();
     if (tid < 32) used[tid] = 0u;
     if (tid == 0) base_sh = 0;
     __syncthreads();
@@ -87,10 +87,9 @@ __global__ void __launch_bounds__(GROUP_THREADS) grouping_kernel(const int *__re
 }
 
 int launch_grouping(cudaStream_t s, const int *picks, int rows, int slots, int E1, int maxm, int *ids, int *count,
-                    int *members) {
-    grouping_kernel<<<E1, GROUP_THREADS, 0, s>>>(picks, rows, slots, E1, maxm, ids, count, members);
-    GF_CUDA(cudaGetLastError());
-    return 0;
+                    int *members, bool pdl) {
+    return launch_k(grouping_kernel, dim3(E1), dim3(GROUP_THREADS), 0, s, pdl, picks, rows, slots, E1, maxm, ids, count,
+                    members);
 }
 }  // namespace gf
 
@@ -132,7 +131,7 @@ extern "C" int glmflash_grouping_run(glmflash_grouping *g, void *stream, const i
     GF_REQUIRE(g && picks, "null argument");
     GF_REQUIRE(rows > 0 && rows <= g->cfg.max_rows, "grouping rows exceed scratch");
     return launch_grouping((cudaStream_t)stream, picks, rows, g->cfg.slots, g->cfg.experts + 1, g->cfg.max_rows, g->ids,
-                           g->count, g->members);
+                           g->count, g->members, g->cfg.pdl != 0);
 }
 
 extern "C" const int32_t *glmflash_grouping_ids(const glmflash_grouping *g) { return g ? g->ids : nullptr; }

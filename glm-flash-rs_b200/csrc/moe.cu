@@ -14,8 +14,8 @@ int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limi
 __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
                                                       const float *__restrict__ route_w, float *__restrict__ out, int rows,
                                                       int slots, int H, int E, int shared_exl3, int e_lo, int e_hi) {
-    pdl_launch_dependents();
     pdl_wait();
+    pdl_launch_dependents();
     const int r = blockIdx.y;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (d >= H) return;
@@ -47,10 +47,8 @@ __global__ void __launch_bounds__(256) rank_sum_kernel(const float *__restrict__
 int launch_combine(cudaStream_t s, const float *Y, const int *picks, const float *route_w, float *out, int rows,
                    const glmflash_config &c) {
     const dim3 grid((unsigned)((c.hidden / 4 + 255) / 256), (unsigned)rows);
-    combine_kernel<<<grid, 256, 0, s>>>(Y, picks, route_w, out, rows, c.slots, c.hidden, c.experts, c.shared_exl3,
-                                        c.expert_lo, c.expert_hi);
-    GF_CUDA(cudaGetLastError());
-    return 0;
+    return launch_k(combine_kernel, grid, dim3(256), 0, s, c.pdl != 0, Y, picks, route_w, out, rows, c.slots, c.hidden,
+                    c.experts, c.shared_exl3, c.expert_lo, c.expert_hi);
 }
 }  // namespace gf
 

@@ -56,7 +56,10 @@ typedef struct glmflash_config {
     int32_t expert_lo;     /* expert-parallel window: of the routed experts only ids in [expert_lo,        */
     int32_t expert_hi;     /* expert_hi) are computed here (0, E = all of them)                            */
     float   limit;         /* SwiGLU clamp (upstream 10.0, src/experts.rs:521)                             */
-    int32_t reserved[7];
+    int32_t pdl;           /* 1: chain the kernels of a run with programmatic dependent launch, so that each
+                              kernel's weight prefetch overlaps its predecessor's tail (upstream's "pdl" load
+                              policy, src/experts.rs:350-354, native/expert_loads.cu:38-44); 0: plain launches */
+    int32_t reserved[6];
 } glmflash_config;
 
 /* The nine tensors `m.pointer(..moe.experts.*)` resolves upstream (src/experts.rs:467). */
@@ -87,7 +90,7 @@ int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, const uint32
  * reference.  It exists for hosts that took over the whole device heap at start-up (so a later cudaMalloc by a
  * library would fail or fragment their pool) and for serving loops where an allocator call would stall every
  * stream of the device.  The scratch is a fixed array inside the library (glmflash_exl3_linear_static_max_bytes(),
- * 1.125 MiB, held by every GPU that loads the library until the process exits), so shapes are limited to
+ * 2.125 MiB, held by every GPU that loads the library until the process exits), so shapes are limited to
  * K <= 2048 and N <= 2048; larger shapes are rejected with an error.  The call itself allocates nothing.
  * The first call on a device looks up the array's device address (a one-time, per-device set-up step): make that
  * first call outside any stream capture.  All calls share the one array and it keeps the previous call's

@@ -1,0 +1,77 @@
+"""Expert-parallel layer on 2 GPUs (NCCL over NVLink): every rank ends with the bytes of the rank-ordered sum, and
+they equal the single-GPU layer output within fp32 re-association.  Skipped with fewer than 2 GPUs."""
+import os
+import socket
+import sys
+
+import numpy as np
+import pytest
+
+from conftest import ROOT, rel_err
+
+pytestmark = pytest.mark.gpu
+
+H, I, E, S = 2048, 1536, 64, 5
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, rows_list, q):
+    sys.path.insert(0, ROOT)
+    os.environ["NCCL_NVLS_ENABLE"] = "0"
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    from glmflash_b200 import ep, synth
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        res = []
+        for rows in rows_list:
+            layer = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev)
+            single = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows))
+            for l in range(2):
+                bank = synth.device_bank(300 + l, H, I, E, dev)
+                x = torch.from_numpy(synth.activations_bf16(310 + l, rows, H).view(np.int16)).to(dev).view(torch.bfloat16)
+                picks, rw = synth.route(320 + l, rows, E, S - 1, shared_bias=rows <= 16, uniform=rows > 16)
+                pd, wd = torch.from_numpy(picks).to(dev), torch.from_numpy(rw).to(dev)
+                out = layer.run(l, bank, x, pd, wd, rows).clone()
+                single.run(bank, x, pd, wd, rows)
+                torch.cuda.synchronize()
+                ref = single.output[:rows].clone()
+                chk = [torch.empty_like(out) for _ in range(world)]
+                dist.all_gather(chk, out)
+                same = all(torch.equal(chk[0], c) for c in chk)
+                res.append((rows, l, same, rel_err(out.cpu().numpy(), ref.cpu().numpy())[0]))
+        q.put((rank, res))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ep_two_gpus(cuda):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    world = 2
+    procs = [ctx.Process(target=_worker, args=(r, world, port, [1, 16, 300], q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=600)
+        assert p.exitcode == 0
+    for _ in range(world):
+        rank, res = q.get(timeout=5)
+        for rows, l, same, err in res:
+            assert same, (rank, rows, l, "ranks disagree")
+            assert err < 1e-5, (rank, rows, l, err)

@@ -146,6 +146,28 @@ def test_graph_replay_is_byte_equal(pkg, oracle, synth, cuda, dbank):
         assert (ex.y[: rows * S].cpu().numpy().view(np.uint32) == eager.view(np.uint32)).all()
 
 
+def test_pdl_chain_equals_plain_launches(pkg, oracle, synth, cuda, dbank):
+    """Programmatic dependent launch only moves prologues earlier: bytes are those of plain launches, also when the
+    layer is replayed back to back (the next layer's grouping overlaps this layer's combine)."""
+    import torch
+    rows = 7
+    outs = {}
+    for pdl in (0, 1):
+        moe = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=8, pdl=pdl))
+        res = []
+        for it in range(3):
+            x = synth.activations_bf16(400 + it, rows, H)
+            picks, rw = synth.route(410 + it, rows, E, S - 1, shared_bias=True)
+            args = (dbank, _bf16_dev(x, cuda), torch.from_numpy(picks).to(cuda), torch.from_numpy(rw).to(cuda), rows)
+            for _ in range(3):                                  # back to back: kernels of consecutive runs overlap
+                moe.run(*args)
+            torch.cuda.synchronize()
+            res.append(moe.output[:rows].cpu().numpy().copy())
+        outs[pdl] = np.stack(res)
+    assert np.isfinite(outs[1]).all()
+    assert (outs[0].view(np.uint32) == outs[1].view(np.uint32)).all()
+
+
 def test_vs_upstream_kernels(pkg, oracle, synth, cuda, bank_scaled, dbank_scaled):
     """The upstream CUDA kernels, compiled unmodified for sm_100a, on the same tensors: Xd and Y agree within
     the tolerance, and the oracle agrees with upstream's GPU result (this pins the oracle to the reference)."""
