@@ -10,7 +10,7 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SO_PATH = os.path.join(_HERE, "libglmflash_b200.so")
+SO_PATH = os.environ.get("GLMFLASH_B200_SO") or os.path.join(_HERE, "libglmflash_b200.so")
 
 
 class Config(C.Structure):

@@ -34,19 +34,35 @@ int fail_cuda(cudaError_t e, const char *what);
 // Launch with or without the programmatic-dependent-launch attribute (the kernel's griddepcontrol instructions
 // are no-ops without it).
 template <typename... KArgs, typename... Args>
-int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, Args... args) {
+int launch_kc(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, size_t smem, cudaStream_t s, bool pdl,
+              Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute at[1];
-    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = pdl ? at : nullptr;
-    cfg.numAttrs = pdl ? 1 : 0;
+    cudaLaunchAttribute at[2];
+    int n = 0;
+    if (pdl) {
+        at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster.x * cluster.y * cluster.z > 1) {
+        at[n].id = cudaLaunchAttributeClusterDimension;
+        at[n].val.clusterDim.x = cluster.x;
+        at[n].val.clusterDim.y = cluster.y;
+        at[n].val.clusterDim.z = cluster.z;
+        ++n;
+    }
+    cfg.attrs = n ? at : nullptr;
+    cfg.numAttrs = n;
     GF_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
     return 0;
+}
+template <typename... KArgs, typename... Args>
+int launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl, Args... args) {
+    return launch_kc(kernel, grid, block, dim3(1, 1, 1), smem, s, pdl, args...);
 }
 
 // ---- codebook ------------------------------------------------------------------------------------------
@@ -142,6 +158,18 @@ __device__ __forceinline__ void tma_load_1d(void *dst_smem, const void *src_gmem
                      smem_u32(dst_smem)),
                  "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
+}
+
+// Thread-block cluster: barrier over all threads of the cluster, and the address of a peer CTA's copy of a shared
+// memory object (distributed shared memory).  A cluster of one CTA is its own peer.
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+template <typename Tp>
+__device__ __forceinline__ const Tp *cluster_map(const Tp *p, uint32_t rank) {
+    uint64_t out;
+    asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"((uint64_t)p), "r"(rank));
+    return reinterpret_cast<const Tp *>(out);
 }
 
 // Programmatic dependent launch: let the next kernel of the stream start its prologue; wait until the

@@ -24,26 +24,27 @@ int launch_rot_in(cudaStream_t s, const void *x, bool x_is_bf16, int x_stride, c
                     out0, out1, K, slots, P, mats, E, shared_exl3, e_lo, e_hi);
 }
 
-int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax, bool pdl) {
+int launch_gemv(cudaStream_t s, int mats, GemvArgs a, int umax, bool pdl) {
     const int sets = a.maxm > 8 ? 2 : 1;
-    const size_t smem = gemv_smem_bytes(mats, sets);
-    static bool configured_dev[64] = {};
+    gemv_split(a.K, a.KTC, a.SK);
+    const size_t smem = gemv_smem_bytes(mats, sets, a.KTC);
+    GF_REQUIRE(smem <= 200 * 1024, "K is too large for the decode path's shared-memory staging");
+    static size_t configured[64][4] = {};
     int dev = 0;
     GF_CUDA(cudaGetDevice(&dev));
-    bool &configured = configured_dev[dev & 63];
-    if (!configured) {
-        if (set_smem(gemv_kernel<2, 1>, gemv_smem_bytes(2, 1))) return -1;
-        if (set_smem(gemv_kernel<2, 2>, gemv_smem_bytes(2, 2))) return -1;
-        if (set_smem(gemv_kernel<1, 1>, gemv_smem_bytes(1, 1))) return -1;
-        if (set_smem(gemv_kernel<1, 2>, gemv_smem_bytes(1, 2))) return -1;
-        configured = true;
+    size_t &have = configured[dev & 63][(mats - 1) * 2 + (sets - 1)];
+    if (have < smem) {                             // raise the dynamic shared-memory limit of this instantiation once
+        if (mats == 2 && sets == 1) { if (set_smem(gemv_kernel<2, 1>, smem)) return -1; }
+        else if (mats == 2) { if (set_smem(gemv_kernel<2, 2>, smem)) return -1; }
+        else if (sets == 1) { if (set_smem(gemv_kernel<1, 1>, smem)) return -1; }
+        else { if (set_smem(gemv_kernel<1, 2>, smem)) return -1; }
+        have = smem;
     }
-    const dim3 grid((unsigned)(a.N / 128), (unsigned)a.SK, (unsigned)umax);
-    const dim3 block(GEMV_THREADS);
-    if (mats == 2 && sets == 1) return launch_k(gemv_kernel<2, 1>, grid, block, smem, s, pdl, a);
-    if (mats == 2) return launch_k(gemv_kernel<2, 2>, grid, block, smem, s, pdl, a);
-    if (sets == 1) return launch_k(gemv_kernel<1, 1>, grid, block, smem, s, pdl, a);
-    return launch_k(gemv_kernel<1, 2>, grid, block, smem, s, pdl, a);
+    const dim3 grid((unsigned)(a.N / 128), (unsigned)a.SK, (unsigned)umax), block(GEMV_THREADS), cluster(1, a.SK, 1);
+    if (mats == 2 && sets == 1) return launch_kc(gemv_kernel<2, 1>, grid, block, cluster, smem, s, pdl, a);
+    if (mats == 2) return launch_kc(gemv_kernel<2, 2>, grid, block, cluster, smem, s, pdl, a);
+    if (sets == 1) return launch_kc(gemv_kernel<1, 1>, grid, block, cluster, smem, s, pdl, a);
+    return launch_kc(gemv_kernel<1, 2>, grid, block, cluster, smem, s, pdl, a);
 }
 
 int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit) {
@@ -69,9 +70,8 @@ using namespace gf;
 struct glmflash_experts {
     glmflash_config cfg;
     __half *xg = nullptr, *xu = nullptr, *xd = nullptr;
-    float *z = nullptr, *y = nullptr;
-    int *tickets = nullptr, *status = nullptr;
-    int sk_gu = 0, sk_dn = 0;
+    float *y = nullptr;
+    int *status = nullptr;
     int phases = 7;                                 // profiling aid: 1 = input rotation, 2 = gate/up, 4 = down
 };
 
@@ -82,19 +82,14 @@ extern "C" int glmflash_experts_new(const glmflash_config *cfg, size_t cfg_bytes
     glmflash_experts *e = new (std::nothrow) glmflash_experts();
     GF_REQUIRE(e != nullptr, "out of host memory");
     e->cfg = *cfg;
-    const size_t H = cfg->hidden, I = cfg->inter, P = (size_t)cfg->max_rows * cfg->slots, E1 = cfg->experts + 1;
-    e->sk_gu = cfg->hidden / GEMV_KC;
-    e->sk_dn = cfg->inter / GEMV_KC;
-    const size_t zf = std::max((size_t)2 * e->sk_gu * P * I, (size_t)e->sk_dn * P * H);
-    const size_t nbmax = std::max(H, I) / 128;
+    const size_t H = cfg->hidden, I = cfg->inter, P = (size_t)cfg->max_rows * cfg->slots;
     auto alloc = [&](void **p, size_t bytes) -> int {
         GF_CUDA(cudaMalloc(p, bytes));
         GF_CUDA(cudaMemset(*p, 0, bytes));
         return 0;
     };
     if (alloc((void **)&e->xg, P * H * 2) || alloc((void **)&e->xu, P * H * 2) || alloc((void **)&e->xd, P * I * 2) ||
-        alloc((void **)&e->z, zf * 4) || alloc((void **)&e->y, P * H * 4) ||
-        alloc((void **)&e->tickets, E1 * nbmax * 4) || alloc((void **)&e->status, 4)) {
+        alloc((void **)&e->y, P * H * 4) || alloc((void **)&e->status, 4)) {
         glmflash_experts_free(e);
         return -1;
     }
@@ -104,8 +99,7 @@ extern "C" int glmflash_experts_new(const glmflash_config *cfg, size_t cfg_bytes
 
 extern "C" void glmflash_experts_free(glmflash_experts *e) {
     if (!e) return;
-    cudaFree(e->xg); cudaFree(e->xu); cudaFree(e->xd); cudaFree(e->z); cudaFree(e->y);
-    cudaFree(e->tickets); cudaFree(e->status);
+    cudaFree(e->xg); cudaFree(e->xu); cudaFree(e->xd); cudaFree(e->y); cudaFree(e->status);
     delete e;
 }
 
@@ -128,19 +122,19 @@ extern "C" int glmflash_experts_run_rows(glmflash_experts *e, void *stream, cons
         return -1;
     GemvArgs a{};
     a.ids = ids; a.count = count; a.members = members;
-    a.Z = e->z; a.tickets = e->tickets; a.status = e->status;
+    a.status = e->status;
     a.P = P; a.maxm = maxm; a.slots = c.slots; a.E = c.experts; a.e_lo = c.expert_lo; a.e_hi = c.expert_hi;
     a.shared_exl3 = c.shared_exl3; a.limit = c.limit;
     // gate + up, SwiGLU, down-input rotation -> xd
     a.X0 = e->xg; a.X1 = e->xu; a.T0 = w->gt; a.T1 = w->ut;
     a.sv0 = (const __half *)w->svh_g; a.sv1 = (const __half *)w->svh_u; a.sd = (const __half *)w->suh_d;
-    a.xd = e->xd; a.y = nullptr; a.K = H; a.N = I; a.SK = e->sk_gu; a.mode = GEMV_GATEUP;
+    a.xd = e->xd; a.y = nullptr; a.K = H; a.N = I; a.mode = GEMV_GATEUP;
     if ((e->phases & 2) && launch_gemv(s, 2, a, umax, pdl)) return -1;
     if (!(e->phases & 4)) return 0;
     // down -> y
     a.X0 = e->xd; a.X1 = e->xd; a.T0 = w->dt; a.T1 = w->dt;
     a.sv0 = (const __half *)w->svh_d; a.sv1 = nullptr; a.sd = nullptr;
-    a.xd = nullptr; a.y = e->y; a.K = I; a.N = H; a.SK = e->sk_dn; a.mode = GEMV_DOWN;
+    a.xd = nullptr; a.y = e->y; a.K = I; a.N = H; a.mode = GEMV_DOWN;
     return launch_gemv(s, 1, a, umax, pdl);
 }
 
@@ -157,15 +151,14 @@ extern "C" const int32_t *glmflash_experts_status(const glmflash_experts *e) { r
 // ---- single EXL3 linear (fp16 in, fp16 out): rot_in + one-matrix GEMV with the fp16 epilogue ---------------
 namespace {
 struct LinearScratch {
-    size_t xr, z, tickets, tables, total;
+    size_t xr, tables, total;
 };
 LinearScratch linear_layout(int K, int N) {
+    (void)N;
     LinearScratch L;
     size_t off = 0;
     auto take = [&](size_t bytes) { size_t o = off; off += (bytes + 255) / 256 * 256; return o; };
-    L.xr = take((size_t)16 * K * 2);
-    L.z = take((size_t)(K / GEMV_KC) * 16 * N * 4);   // [SK][16 rows][N]
-    L.tickets = take((size_t)(N / 128) * 4);
+    L.xr = take((size_t)16 * K * 2);                // rotated input rows
     L.tables = take((size_t)(2 + 16) * 4 + 4);      // ids[1], count[1], members[16], status
     L.total = off;
     return L;
@@ -193,7 +186,6 @@ extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, c
     const LinearScratch L = linear_layout(K, N);
     unsigned char *base = (unsigned char *)scratch;
     int *tables = (int *)(base + L.tables);
-    GF_CUDA(cudaMemsetAsync(base + L.tickets, 0, (size_t)(N / 128) * 4, s));
     linear_tables_kernel<<<1, 32, 0, s>>>(tables, rows);
     GF_CUDA(cudaGetLastError());
     __half *xr = (__half *)(base + L.xr);
@@ -202,9 +194,9 @@ extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, c
     GemvArgs a{};
     a.X0 = xr; a.X1 = xr; a.T0 = words; a.T1 = words;
     a.ids = tables; a.count = tables + 1; a.members = tables + 2;
-    a.Z = (float *)(base + L.z); a.tickets = (int *)(base + L.tickets); a.status = tables + 18;
+    a.status = tables + 18;
     a.sv0 = (const __half *)svh; a.xd = (__half *)y;
-    a.K = K; a.N = N; a.P = rows; a.SK = K / GEMV_KC; a.maxm = rows; a.slots = 1; a.E = 1; a.e_lo = 0; a.e_hi = 1;
+    a.K = K; a.N = N; a.P = rows; a.maxm = rows; a.slots = 1; a.E = 1; a.e_lo = 0; a.e_hi = 1;
     a.shared_exl3 = 1; a.mode = GEMV_LINEAR; a.limit = 10.f;
     return launch_gemv(s, 1, a, 1, false);
 }
@@ -216,8 +208,8 @@ extern "C" int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, c
 // and for latency-critical loops in which a cudaMalloc/cudaFree would serialise the device behind the allocator.
 // The array is part of every loaded copy of the library: each GPU that loads it holds these bytes until exit.
 namespace {
-constexpr int STATIC_LINEAR_MAX_K = 2048, STATIC_LINEAR_MAX_N = 2048;
-constexpr size_t STATIC_LINEAR_BYTES = 2228224;           // 2.125 MiB >= linear_layout(2048, 2048).total
+constexpr int STATIC_LINEAR_MAX_K = 4096;
+constexpr size_t STATIC_LINEAR_BYTES = 135168;            // 132 KiB >= linear_layout(4096, N).total
 static __device__ __align__(256) unsigned char g_static_linear_scratch[STATIC_LINEAR_BYTES];
 void *g_static_linear_ptr[64] = {};                       // device address of the array, per device ordinal
 }  // namespace
@@ -227,8 +219,8 @@ extern "C" size_t glmflash_exl3_linear_static_max_bytes(void) { return STATIC_LI
 extern "C" int glmflash_exl3_linear_static(void *stream, const uint16_t *x, int rows, const uint32_t *words,
                                            const uint16_t *suh, const uint16_t *svh, int K, int N, uint16_t *y) {
     GF_REQUIRE(K > 0 && K % 256 == 0 && N > 0 && N % 128 == 0, "K must be a multiple of 256 and N of 128");
-    GF_REQUIRE(K <= STATIC_LINEAR_MAX_K && N <= STATIC_LINEAR_MAX_N,
-               "shape exceeds the built-in scratch (K <= 2048, N <= 2048): use glmflash_exl3_linear with caller scratch");
+    GF_REQUIRE(K <= STATIC_LINEAR_MAX_K,
+               "shape exceeds the built-in scratch (K <= 4096): use glmflash_exl3_linear with caller scratch");
     GF_REQUIRE(linear_layout(K, N).total <= STATIC_LINEAR_BYTES, "shape exceeds the built-in scratch");
     int dev = 0;
     GF_CUDA(cudaGetDevice(&dev));

@@ -4,8 +4,8 @@
 // (native/exl3.cu:59-170,260-321, native/expert_loads.cu:130-285).  Same operands and the same member /
 // pair conventions; a different machine mapping:
 //
-//   * work item = (distinct expert u, 128-column block nb, K split): MATS matrices x 8 k-tiles x 8 n-tiles,
-//     i.e. MATS x 8 contiguous 1-KB rows of packed trellis words.  One elected warp issues them all as TMA
+//   * work item = (distinct expert u, 128-column block nb, K split): MATS matrices x 16 k-tiles x 8 n-tiles,
+//     i.e. MATS x 16 contiguous 1-KB rows of packed trellis words.  One elected warp issues them all as TMA
 //     bulk copies (cp.async.bulk) into shared memory at kernel start, four k-tiles per mbarrier, so the whole
 //     item is in flight before anything else happens and the copy engine, not the warps, follows the stream.
 //   * a lane reads 16 bytes (4 words of one tile) with one LDS.128: that is 32 weights, all 16 k of two
@@ -18,10 +18,11 @@
 //     (w, w) meets (x_k, 0), so a.w is accumulated once, in fp32.  Members (<= 8 per set) are the N dimension;
 //     a second set of B operands serves experts with 9..16 members without decoding twice.
 //   * warps of a CTA own disjoint n-tiles (and matrices / K halves), so nothing is reduced across warps by
-//     atomics; the K splits of an (expert, column block) meet through an fp32 partial buffer Z and the CTA
-//     that arrives last (one atomic ticket per item, reset by the last arriver so graphs replay) sums them in
-//     ascending split order and runs the epilogue: Hadamard, scales, SwiGLU, down-input rotation (MATS = 2)
-//     or Hadamard and output scale (MATS = 1).  No output element depends on arrival order.
+//     atomics; the K splits of an (expert, column block) are the CTAs of one thread-block cluster: each leaves its
+//     fp32 partial in its own shared memory, and after a cluster barrier the members are finished by the CTAs
+//     round robin, reading the peers' partials through distributed shared memory and adding them in ascending
+//     split order before the epilogue: Hadamard, scales, SwiGLU, down-input rotation (MATS = 2) or Hadamard and
+//     output scale (MATS = 1).  No global scratch, no atomics, no value depends on arrival order.
 //   * every pair's result depends only on its own row: the split count and tiling are fixed by the shape, and
 //     mma keeps columns (members) independent, so a row of a 16-row window has the bits of the 1-row call.
 #pragma once
@@ -29,12 +30,14 @@
 
 namespace gf {
 
-constexpr int GEMV_THREADS = 128;
-constexpr int GEMV_KTC = 8;                        // k-tiles per CTA item (per matrix)
-constexpr int GEMV_KC = GEMV_KTC * 16;             // 128 k per CTA item
-constexpr int GEMV_GROUPS = GEMV_KTC / 4;          // mbarriers (4 k-tiles each)
+// GF_PROBE (timing experiments only, wrong results, in the spirit of upstream's PROBE modes,
+// native/expert_loads.cu:46-47): 1 = no decode / mma, 2 = no partial exchange and epilogue, 3 = both.
+#ifndef GF_PROBE
+#define GF_PROBE 0
+#endif
+constexpr int GEMV_THREADS = 256;
+constexpr int GEMV_MAX_SPLITS = 8;                 // K splits of an item = CTAs of a cluster (portable maximum)
 constexpr int GEMV_WROW = 1024 + 32;               // bytes per staged weight row (1 KB + 32 B: conflict-free LDS.128)
-constexpr int GEMV_AST = GEMV_KC + 8;              // dwords per staged activation row (+32 B pad)
 constexpr int GEMV_PST = 132;                      // floats per partial row
 
 enum GemvMode : int { GEMV_GATEUP = 0, GEMV_DOWN = 1, GEMV_LINEAR = 2 };
@@ -43,13 +46,11 @@ struct GemvArgs {
     const __half *X0, *X1;        // rotated inputs [P][K] fp16 (X1: second matrix, MATS = 2)
     const uint32_t *T0, *T1;      // trellis banks [E1][K/16][N/16][32]
     const int *ids, *count, *members;
-    float *Z;                     // [MATS][SK][P][N] fp32 partials
-    int *tickets;                 // [E1][N/128]
     const __half *sv0, *sv1, *sd; // gate/up: svh_g, svh_u, suh_d;  down / linear: svh_d
     __half *xd;                   // gate/up out: [P][N] fp16;  linear out: [P][N] fp16
     float *y;                     // down out: [P][N] fp32
     int *status;
-    int K, N, P, SK, maxm, slots, E, e_lo, e_hi, shared_exl3, mode;
+    int K, N, P, SK, KTC, maxm, slots, E, e_lo, e_hi, shared_exl3, mode;
     float limit;
 };
 
@@ -65,33 +66,39 @@ __device__ __forceinline__ uint32_t weight_dup(uint32_t x) {
     return *reinterpret_cast<const uint32_t *>(&r);
 }
 
+// K split of a shape: k-tiles per CTA (a multiple of 16) and the number of splits (<= 8, the cluster size)
+inline void gemv_split(int K, int &ktc, int &sk) {
+    ktc = 16;
+    while ((K / 16) / ktc > GEMV_MAX_SPLITS) ktc *= 2;
+    sk = (K / 16) / ktc;
+}
 // dynamic shared memory size of a launch
-inline size_t gemv_smem_bytes(int mats, int sets) {
-    size_t w = (size_t)mats * GEMV_KTC * GEMV_WROW;
+inline size_t gemv_smem_bytes(int mats, int sets, int ktc) {
+    size_t w = (size_t)mats * ktc * GEMV_WROW;
     size_t part = (size_t)2 * sets * 8 * GEMV_PST * sizeof(float);
-    size_t a = (size_t)mats * sets * 8 * GEMV_AST * 4;
-    return 64 + (w > part ? w : part) + a;
+    size_t a = (size_t)mats * sets * 8 * (ktc * 16 + 8) * 4;
+    return 128 + (w > part ? w : part) + a;
 }
 
-// Work item (CTA) = (distinct expert u, 128-column block nb, K split of 128): MATS x 8 rows of 1 KB.
-// 4 warps.  MATS = 2: warp = (matrix, half of the 8 n-tiles), both 4-k-tile groups.  MATS = 1: warp = (group, half).
+// Work item (cluster) = (distinct expert u, 128-column block nb); CTA r of the cluster owns K split r: MATS x KTC rows
+// of 1 KB.  8 warps.  MATS = 2: warp = (matrix, pair of n-tiles), all k groups.  MATS = 1: warp = (K half, pair).
 template <int MATS, int SETS>
-__global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 8 : 5) gemv_kernel(const GemvArgs a) {
+__global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(const GemvArgs a) {
     extern __shared__ __align__(128) unsigned char smem[];
-    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                         // one barrier per 4 k-tiles
-    unsigned char *wsm = smem + 64;                                              // [MATS][8] rows of GEMV_WROW
-    constexpr size_t WBYTES = (size_t)MATS * GEMV_KTC * GEMV_WROW;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                         // one barrier per 4 k-tiles (<= 16)
+    unsigned char *wsm = smem + 128;                                             // [MATS][KTC] rows of GEMV_WROW
+    const int KTC = a.KTC, NG = KTC >> 2, KC = KTC * 16, AST = KC + 8;
+    const size_t wbytes = (size_t)MATS * KTC * GEMV_WROW;
     constexpr size_t PBYTES = (size_t)2 * SETS * 8 * GEMV_PST * sizeof(float);
-    constexpr size_t WP = WBYTES > PBYTES ? WBYTES : PBYTES;
+    const size_t wp = wbytes > PBYTES ? wbytes : PBYTES;
     float *part = reinterpret_cast<float *>(wsm);                                // aliases wsm after the K loop
-    uint32_t *asm_ = reinterpret_cast<uint32_t *>(wsm + WP);                     // [MATS][SETS*8][GEMV_AST]
+    uint32_t *asm_ = reinterpret_cast<uint32_t *>(wsm + wp);                     // [MATS][SETS*8][AST]
     __shared__ int rows_sh[16];
-    __shared__ int last_sh;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = lane >> 2, T = lane & 3;
-    const int nb = blockIdx.x, split = blockIdx.y, u = blockIdx.z;
-    const int KT = a.K >> 4, NTILES = a.N >> 4, NB = a.N >> 7;
+    const int nb = blockIdx.x, split = blockIdx.y, u = blockIdx.z;               // split == rank in the cluster
+    const int KT = a.K >> 4, NTILES = a.N >> 4;
 
     // one round trip for everything the prologue needs (none of the three loads depends on another)
     const int cnt = __ldcg(a.count);
@@ -99,64 +106,60 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 8 : 5) gemv_kernel(c
     int code = -1;
     if (tid < 16 && tid < a.maxm) code = __ldcg(a.members + (size_t)u * a.maxm + tid);
     if (tid == 0) {
-#pragma unroll
-        for (int g = 0; g < GEMV_GROUPS; ++g) mbar_init(bars + g, 1);
+        for (int g = 0; g < NG; ++g) mbar_init(bars + g, 1);
         mbar_fence_init();
     }
-    if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the CTA
+    if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
     if (tid < 16) rows_sh[tid] = code >= 0 ? (code >> 5) * a.slots + (code & 31) : -1;
     __syncthreads();
 
     // ---- the whole item's packed words, in flight at once
-    const int kt0 = split * GEMV_KTC;
+    const int kt0 = split * KTC;
     if (warp == 0) {
-        if (lane == 0) {
-#pragma unroll
-            for (int g = 0; g < GEMV_GROUPS; ++g) mbar_expect_tx(bars + g, MATS * 4 * 1024);
-        }
+        if (lane == 0)
+            for (int g = 0; g < NG; ++g) mbar_expect_tx(bars + g, MATS * 4 * 1024);
         __syncwarp();
-        if (lane < MATS * GEMV_KTC) {
-            const int mat = lane / GEMV_KTC, ktl = lane % GEMV_KTC;
+        for (int r = lane; r < MATS * KTC; r += 32) {
+            const int mat = r / KTC, ktl = r % KTC;
             const uint32_t *T_ = mat ? a.T1 : a.T0;
             const uint32_t *src = T_ + (((size_t)e * KT + kt0 + ktl) * NTILES + (size_t)nb * 8) * 32;
-            tma_load_1d(wsm + (size_t)lane * GEMV_WROW, src, 1024, bars + (ktl >> 2));
+            tma_load_1d(wsm + (size_t)r * GEMV_WROW, src, 1024, bars + (ktl >> 2));
         }
     }
     pdl_launch_dependents();
     int nmem = 0;
 #pragma unroll
     for (int m = 0; m < SETS * 8; ++m) nmem += rows_sh[m] >= 0;   // members come first
-    pdl_wait();                                   // X / Z / tickets belong to the kernels before this one
+    pdl_wait();                                   // X belongs to the kernel before this one
 
     // ---- stage the members' activations of this K range as (x_k, 0) pairs, permuted to the mma order:
     //      dword position of local k = 64 g + 16 T + 8 h + 2 t + b  is  g*64 + (2t + h)*8 + 2T + b.
     //      Rows of absent members are left as they are: an mma column depends on its own B column only, and the
     //      columns of absent members are never stored.
     {
-        const int k0 = kt0 * 16;
-        const int items = MATS * nmem * (GEMV_KC / 2);
+        const int k0 = kt0 * 16, half = KC >> 1;
+        const int items = MATS * nmem * half;
         for (int i = tid; i < items; i += GEMV_THREADS) {
-            const int kp = i % (GEMV_KC / 2), mm = i / (GEMV_KC / 2);
+            const int kp = i % half, mm = i / half;
             const int m = mm % nmem, mat = mm / nmem;
             const int p = rows_sh[m];
             const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>((mat ? a.X1 : a.X0) + (size_t)p * a.K + k0) + kp);
             const int kl = 2 * kp;
             const int g = kl >> 6, TT = (kl >> 4) & 3, h = (kl >> 3) & 1, t = (kl >> 1) & 3;
             const int pos = g * 64 + (2 * t + h) * 8 + 2 * TT;
-            *reinterpret_cast<uint2 *>(asm_ + ((size_t)mat * SETS * 8 + m) * GEMV_AST + pos) =
-                make_uint2(v & 0xffffu, v >> 16);
+            *reinterpret_cast<uint2 *>(asm_ + ((size_t)mat * SETS * 8 + m) * AST + pos) = make_uint2(v & 0xffffu, v >> 16);
         }
     }
     __syncthreads();
 
     // ---- K loop
-    const int sub = warp >> 1, nth = warp & 1;
+    const int sub = warp >> 2, ntp = warp & 3;
     const int mat = MATS == 2 ? sub : 0;
-    const int g_begin = MATS == 2 ? 0 : sub, g_end = MATS == 2 ? GEMV_GROUPS : sub + 1;
+    const int g_begin = MATS == 2 ? 0 : sub * (NG >> 1), g_end = MATS == 2 ? NG : (sub + 1) * (NG >> 1);
     const bool two_sets = SETS == 2 && nmem > 8;
-    float acc[4][SETS][4];
+    float acc[2][SETS][4];
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int n = 0; n < 2; ++n)
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
 #pragma unroll
@@ -169,14 +172,14 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 8 : 5) gemv_kernel(c
         uint2 b[SETS][8];
 #pragma unroll
         for (int s = 0; s < SETS; ++s) {
-            const uint32_t *ar = asm_ + ((size_t)mat * SETS * 8 + s * 8 + G) * GEMV_AST + g * 64 + 2 * T;
+            const uint32_t *ar = asm_ + ((size_t)mat * SETS * 8 + s * 8 + G) * AST + g * 64 + 2 * T;
 #pragma unroll
             for (int m = 0; m < 8; ++m) b[s][m] = *reinterpret_cast<const uint2 *>(ar + m * 8);
         }
         if (!mbar_wait(bars + g, 0)) { ok = false; break; }
-        const unsigned char *wrow = wsm + ((size_t)mat * GEMV_KTC + 4 * g + T) * GEMV_WROW + nth * 512 + G * 16;
+        const unsigned char *wrow = wsm + ((size_t)mat * KTC + 4 * g + T) * GEMV_WROW + ntp * 256 + G * 16;
 #pragma unroll
-        for (int n = 0; n < 4; ++n) {
+        for (int n = 0; n < ((GF_PROBE & 1) ? 0 : 2); ++n) {
             const uint4 wv = *reinterpret_cast<const uint4 *>(wrow + n * 128);
             const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
             const uint32_t before = __shfl_sync(0xffffffffu, wv.w, (lane + 28) & 31);   // word 4G-1 (circular)
@@ -202,60 +205,41 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 8 : 5) gemv_kernel(c
         }
     }
     if (!ok && lane == 0) atomicExch(a.status, GF_STATUS_TMA_TIMEOUT);
+    if (GF_PROBE & 2) {
+        if (acc[0][0][0] == 123.f) a.y[0] = acc[1][0][1];
+        return;
+    }
     __syncthreads();                                // wsm is dead: part aliases it
 
-    // ---- partial[sub][member][column]
+    // ---- this split's partial[sub][member][column] in shared memory, visible to the cluster
 #pragma unroll
-    for (int n = 0; n < 4; ++n)
+    for (int n = 0; n < 2; ++n)
 #pragma unroll
         for (int s = 0; s < SETS; ++s) {
-            const int col = (nth * 4 + n) * 16 + G, mem = s * 8 + 2 * T;
+            const int col = (ntp * 2 + n) * 16 + G, mem = s * 8 + 2 * T;
             float *pp = part + ((size_t)sub * SETS * 8 + mem) * GEMV_PST + col;
             pp[0] = acc[n][s][0];
             pp[GEMV_PST] = acc[n][s][1];
             pp[8] = acc[n][s][2];
             pp[GEMV_PST + 8] = acc[n][s][3];
         }
-    __syncthreads();
-    for (int i = tid; i < MATS * nmem * 32; i += GEMV_THREADS) {
-        const int c4 = i & 31, mm = i >> 5;
-        const int m = mm % nmem, mt = mm / nmem;
-        float4 v = *reinterpret_cast<const float4 *>(part + ((size_t)mt * SETS * 8 + m) * GEMV_PST + 4 * c4);
-        if (MATS == 1) {
-            const float4 w2 = *reinterpret_cast<const float4 *>(part + ((size_t)SETS * 8 + m) * GEMV_PST + 4 * c4);
-            v.x += w2.x; v.y += w2.y; v.z += w2.z; v.w += w2.w;
-        }
-        float *z = a.Z + (((size_t)mt * a.SK + split) * a.P + rows_sh[m]) * a.N + nb * 128 + 4 * c4;
-        __stcg(reinterpret_cast<float4 *>(z), v);
-    }
+    cluster_sync();
 
-    // ---- the last split to arrive sums the partials in split order and finishes the block
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-        int *ticket = a.tickets + (size_t)u * NB + nb;
-        const int prev = atomicAdd(ticket, 1);
-        const int last = prev == a.SK - 1;
-        if (last) *ticket = 0;                    // ready for the next launch or graph replay
-        last_sh = last;
-    }
-    __syncthreads();
-    if (!last_sh) return;
-    __threadfence();
-
-    for (int m = warp; m < nmem; m += GEMV_THREADS / 32) {
+    // ---- member m is finished by CTA m % SK: the splits' partials are read from the peers' shared memory and added
+    //      in split order (for one matrix: K half 0 then 1 inside a split), then the epilogue runs in the warp.
+    for (int m = split + a.SK * warp; m < nmem; m += a.SK * (GEMV_THREADS / 32)) {
         const int p = rows_sh[m];
         const int n0 = nb * 128 + 4 * lane;
         float v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
-        const float *z0 = a.Z + (size_t)p * a.N + n0;
-        const size_t zs = (size_t)a.P * a.N;
-#pragma unroll 4
         for (int s = 0; s < a.SK; ++s) {
-            const float4 q = __ldcg(reinterpret_cast<const float4 *>(z0 + s * zs));
-            v0[0] += q.x; v0[1] += q.y; v0[2] += q.z; v0[3] += q.w;
+            const float *rp = cluster_map(part, s) + (size_t)m * GEMV_PST + 4 * lane;
+            const float4 q = *reinterpret_cast<const float4 *>(rp);
+            const float4 r = *reinterpret_cast<const float4 *>(rp + (size_t)SETS * 8 * GEMV_PST);
             if (MATS == 2) {
-                const float4 r = __ldcg(reinterpret_cast<const float4 *>(z0 + (a.SK + s) * zs));
+                v0[0] += q.x; v0[1] += q.y; v0[2] += q.z; v0[3] += q.w;
                 v1[0] += r.x; v1[1] += r.y; v1[2] += r.z; v1[3] += r.w;
+            } else {
+                v0[0] += q.x + r.x; v0[1] += q.y + r.y; v0[2] += q.z + r.z; v0[3] += q.w + r.w;
             }
         }
         fwht128(v0, lane);
@@ -293,6 +277,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 8 : 5) gemv_kernel(c
             }
         }
     }
+    cluster_sync();                                 // peers may still be reading this CTA's partials
 }
 
 // Input rotation (upstream rot_in_kernel, native/exl3.cu:224-241): one warp per (pair, 128-block, matrix);
@@ -335,6 +320,6 @@ __global__ void __launch_bounds__(256) rot_in_kernel(const IN *__restrict__ x, i
 int launch_rot_in(cudaStream_t s, const void *x, bool x_is_bf16, int x_stride, const int *picks, const __half *suh0,
                   const __half *suh1, __half *out0, __half *out1, int K, int slots, int P, int mats, int E,
                   int shared_exl3, int e_lo, int e_hi, bool pdl);
-int launch_gemv(cudaStream_t s, int mats, const GemvArgs &a, int umax, bool pdl);
+int launch_gemv(cudaStream_t s, int mats, GemvArgs a, int umax, bool pdl);
 
 }  // namespace gf

@@ -90,8 +90,8 @@ int glmflash_exl3_linear(void *stream, const uint16_t *x, int rows, const uint32
  * reference.  It exists for hosts that took over the whole device heap at start-up (so a later cudaMalloc by a
  * library would fail or fragment their pool) and for serving loops where an allocator call would stall every
  * stream of the device.  The scratch is a fixed array inside the library (glmflash_exl3_linear_static_max_bytes(),
- * 2.125 MiB, held by every GPU that loads the library until the process exits), so shapes are limited to
- * K <= 2048 and N <= 2048; larger shapes are rejected with an error.  The call itself allocates nothing.
+ * 132 KiB, held by every GPU that loads the library until the process exits), so shapes are limited to
+ * K <= 4096; larger shapes are rejected with an error.  The call itself allocates nothing.
  * The first call on a device looks up the array's device address (a one-time, per-device set-up step): make that
  * first call outside any stream capture.  All calls share the one array and it keeps the previous call's
  * contents; the call clears what has to start at zero, but two calls that overlap on the GPU (different streams

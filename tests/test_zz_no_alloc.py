@@ -36,10 +36,8 @@ def test_static_linear_matches_scratch_linear_twice(pkg, synth, cuda):
 def test_static_linear_rejects_oversize(pkg, cuda):
     import torch
     L = pkg.lib()
-    assert L.glmflash_exl3_linear_static_max_bytes() >= L.glmflash_exl3_linear_scratch_bytes(2048, 2048) > 0
+    assert L.glmflash_exl3_linear_static_max_bytes() >= L.glmflash_exl3_linear_scratch_bytes(4096, 2048) > 0
     d = torch.zeros(64, dtype=torch.int32, device=cuda)
     p = C.c_void_p(d.data_ptr())
-    rc = L.glmflash_exl3_linear_static(None, p, 1, p, p, p, 4096, 1536, p)
-    assert rc == -1 and b"built-in scratch" in L.glmflash_error()
-    rc = L.glmflash_exl3_linear_static(None, p, 1, p, p, p, 2048, 4096, p)
+    rc = L.glmflash_exl3_linear_static(None, p, 1, p, p, p, 8192, 1536, p)
     assert rc == -1 and b"built-in scratch" in L.glmflash_error()
