@@ -6,25 +6,33 @@
 // fragments in registers.  Here:
 //
 //   plan      one block: members per distinct expert, 128-row M tiles per expert, and the GROUPED row order
-//             (rows of an expert contiguous): src_pair[j] = pair index of grouped row j.
+//             (rows of an expert contiguous): src_pair[j] = pair index of grouped row j.  Work items are
+//             (expert, PAIR of M tiles, 128-column block); an expert with an odd tile count ends with a single.
+//             Pairs come first in the item list, so that the static round-robin over CTAs is balanced.
 //   rot       the input rotation writes Xs[j] = fp16(H(x[row] * suh[e]) / sqrt 128) in grouped order, so the A
 //             operand of every M tile is a contiguous 128 x K slab that one TMA tensor load brings into shared
 //             memory in the 128-byte-swizzled K-major layout the tensor core reads.
-//   gemm      persistent CTAs, one per SM, walk work items (M tile, 128-column block) round robin.  Warp roles:
-//               warp 0      TMA producer of A stages (128 rows x 64 k)
-//               warp 1      issues tcgen05.mma (M 128 x N 128 x K 16, fp16 -> fp32), commits stages and tiles
-//               warp 2      allocates / frees tensor memory
-//               warps 4-7   epilogue: tcgen05.ld one accumulator row (128 fp32) per thread, so the 128-point
-//                           Hadamard transform of the column block runs in the thread's registers; scales, limited
-//                           SwiGLU, down-input rotation; stores fp16 Xd rows (gate/up) or fp32 Y rows (down)
-//               warps 8-15  decode trellis tiles of B (the weights) to fp16 straight into the swizzled K-major
-//                           shared-memory tile (bit-exact codebook; conflict-free 32-bit stores)
-//             A 3- (gate/up) or 6-stage (down) ring of 64-k stages and two accumulator buffers in tensor memory
-//             let the epilogue of one item overlap the main loop of the next.
+//   gemm      persistent CTAs, one per SM, 20 warps:
+//               warp 0       TMA producer of the A stages (two M tiles of 128 rows x 64 k)
+//               warp 1       issues tcgen05.mma (M 128 x N 128 x K 16, fp16 -> fp32), commits stages and passes
+//               warp 2       allocates / frees tensor memory (512 columns)
+//               warps 4-11   epilogue, one accumulator row per thread (tile 0: warps 4-7, tile 1: warps 8-11):
+//                            tcgen05.ld 128 fp32, the 128-point Hadamard transform in the thread's registers,
+//                            scales, limited SwiGLU, down-input rotation; fp16 Xd rows (gate/up) or fp32 Y rows (down)
+//               warps 12-19  decode the trellis tiles of B (the weights) to fp16 straight into the swizzled K-major
+//                            shared-memory tile (bit-exact codebook; conflict-free 32-bit stores); the packed words
+//                            of the next stage are already in registers while a stage is decoded
+//             A decoded B stage serves BOTH M tiles of the item (256 rows), which halves the decode work per
+//             flop.  The gate and the up projection of an item are two PASSES over K with their own accumulators
+//             (2 x 128 columns each): while the up pass runs, the epilogue warps turn the gate accumulators into
+//             silu(gate) (kept as bf16 in shared memory), and the up pass's epilogue overlaps the next item's gate
+//             pass, so tensor memory is double-buffered by construction.  Down is one pass per item, alternating
+//             the two accumulator halves.  setmaxnreg moves registers from the producer and decode warpgroups to
+//             the epilogue warpgroups.
 // Arithmetic: one full-K fp32 accumulation chain per output (as upstream's prefill path, which is likewise not
 // bit-equal to its decode path: native/exl3_prefill.cu:20-23), the same transforms and rounding points as
-// upstream's epilogue (native/exl3_prefill.cu:596-622 == native/exl3.cu:260-321).  Deterministic: static work
-// assignment, no atomics; every pair's result depends only on its own row.
+// upstream's epilogue (native/exl3_prefill.cu:596-622 == native/exl3.cu:260-321) with exp / divide in their fast
+// forms.  Deterministic: static work assignment, no atomics; every pair's result depends only on its own row.
 // Every wait is bounded; a wait that gives up raises the abort flag, every role leaves its loops, tensor memory
 // is freed and the status word reports the failure.
 #include <cuda.h>
@@ -37,13 +45,15 @@
 namespace gf {
 int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
 
-constexpr int FG_THREADS = 512;
+constexpr int FG_THREADS = 640;
 constexpr int FG_BM = 128, FG_BN = 128, FG_BK = 64;
 constexpr int FG_TILE_BYTES = FG_BM * FG_BK * 2;           // 16 KB: one 128 x 64 fp16 operand tile
 constexpr int FG_MAXU = 1024;
 
-// plan layout (int32): [0] total M tiles, [1] total grouped rows, [2 .. 2+MAXU] tile_base, [.. +MAXU+1] row_base
-constexpr int PLAN_TILE_BASE = 2, PLAN_ROW_BASE = 2 + FG_MAXU + 1, PLAN_INTS = 2 + 2 * (FG_MAXU + 1);
+// plan layout (int32): [0] total M tiles, [1] total grouped rows, [2] pair items, [3] single items,
+// then three prefix arrays of FG_MAXU + 1 entries: pair_base, single_base, row_base
+constexpr int PLAN_PAIR_BASE = 4, PLAN_SINGLE_BASE = PLAN_PAIR_BASE + FG_MAXU + 1,
+              PLAN_ROW_BASE = PLAN_SINGLE_BASE + FG_MAXU + 1, PLAN_INTS = PLAN_ROW_BASE + FG_MAXU + 1;
 
 // ---------------------------------------------------------------------------------------------- plan
 __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restrict__ ids, const int *__restrict__ count,
@@ -51,7 +61,7 @@ __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restric
                                                           int shared_exl3, int e_lo, int e_hi, int *__restrict__ plan,
                                                           int *__restrict__ src_pair, int *__restrict__ row_expert) {
     __shared__ int cnt_sh[FG_MAXU], row_sh[FG_MAXU], e_sh[FG_MAXU];
-    __shared__ int wsum[2][32];
+    __shared__ int wsum[4][32];
     const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
     const int n = min(count[0], FG_MAXU);
     int cnt = 0, e = -1;
@@ -68,27 +78,31 @@ __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restric
         }
     }
     const int tiles = (cnt + FG_BM - 1) / FG_BM;
-    // block-wide exclusive scans of tiles and cnt
-    int t_inc = tiles, r_inc = cnt;
+    const int pairs = tiles >> 1, single = tiles & 1;
+    // block-wide exclusive scans of pairs, singles, rows (and the tile total)
+    int p_inc = pairs, s_inc = single, r_inc = cnt, t_inc = tiles;
 #pragma unroll
     for (int d = 1; d < 32; d <<= 1) {
-        const int a = __shfl_up_sync(0xffffffffu, t_inc, d), b = __shfl_up_sync(0xffffffffu, r_inc, d);
-        if (lane >= d) { t_inc += a; r_inc += b; }
+        const int a = __shfl_up_sync(0xffffffffu, p_inc, d), b = __shfl_up_sync(0xffffffffu, s_inc, d),
+                  c = __shfl_up_sync(0xffffffffu, r_inc, d), t = __shfl_up_sync(0xffffffffu, t_inc, d);
+        if (lane >= d) { p_inc += a; s_inc += b; r_inc += c; t_inc += t; }
     }
-    if (lane == 31) { wsum[0][warp] = t_inc; wsum[1][warp] = r_inc; }
+    if (lane == 31) { wsum[0][warp] = p_inc; wsum[1][warp] = s_inc; wsum[2][warp] = r_inc; wsum[3][warp] = t_inc; }
     __syncthreads();
-    int t_off = 0, r_off = 0, t_all = 0, r_all = 0;
+    int p_off = 0, s_off = 0, r_off = 0, p_all = 0, s_all = 0, r_all = 0, t_all = 0;
     for (int w = 0; w < 32; ++w) {
-        if (w < warp) { t_off += wsum[0][w]; r_off += wsum[1][w]; }
-        t_all += wsum[0][w]; r_all += wsum[1][w];
+        if (w < warp) { p_off += wsum[0][w]; s_off += wsum[1][w]; r_off += wsum[2][w]; }
+        p_all += wsum[0][w]; s_all += wsum[1][w]; r_all += wsum[2][w]; t_all += wsum[3][w];
     }
-    const int t_ex = t_off + t_inc - tiles, r_ex = r_off + r_inc - cnt;
+    const int p_ex = p_off + p_inc - pairs, s_ex = s_off + s_inc - single, r_ex = r_off + r_inc - cnt;
     cnt_sh[u] = cnt; row_sh[u] = r_ex; e_sh[u] = e;
-    plan[PLAN_TILE_BASE + u] = t_ex;
+    plan[PLAN_PAIR_BASE + u] = p_ex;
+    plan[PLAN_SINGLE_BASE + u] = s_ex;
     plan[PLAN_ROW_BASE + u] = r_ex;
     if (u == 0) {
-        plan[0] = t_all; plan[1] = r_all;
-        plan[PLAN_TILE_BASE + FG_MAXU] = t_all;
+        plan[0] = t_all; plan[1] = r_all; plan[2] = p_all; plan[3] = s_all;
+        plan[PLAN_PAIR_BASE + FG_MAXU] = p_all;
+        plan[PLAN_SINGLE_BASE + FG_MAXU] = s_all;
         plan[PLAN_ROW_BASE + FG_MAXU] = r_all;
     }
     __syncthreads();
@@ -217,7 +231,7 @@ __device__ __forceinline__ void fwht128_regs(float (&v)[128]) {
 }
 
 struct FastGemmArgs {
-    const uint32_t *T0, *T1;       // trellis banks
+    const uint32_t *T0, *T1;       // trellis banks of pass 0 / pass 1 (gate, up;  down: T0 only)
     const int *ids, *plan, *src_pair;
     const __half *sv0, *sv1, *sd;  // gate/up: svh_g, svh_u, suh_d;  down: svh_d
     __half *xd;                    // gate/up out, grouped rows [rows][N]
@@ -227,32 +241,50 @@ struct FastGemmArgs {
     float limit;
 };
 
-struct TileInfo {
-    int u, e, row0, cnt, nb;
+// One work item: expert u (id e), its M tiles tile0 (and tile0 + 1 when ntiles == 2) starting at grouped row row0,
+// cnt0 / cnt1 valid rows in them, column block nb.
+struct ItemInfo {
+    int e, row0, cnt0, cnt1, ntiles, nb;
 };
-__device__ __forceinline__ TileInfo tile_info(int item, int NB, const int *tile_base, const int *row_base, const int *ids, int maxu) {
-    TileInfo t;
-    const int mt = item / NB;
-    t.nb = item % NB;
-    int lo = 0, hi = maxu;                                 // largest u with tile_base[u] <= mt
+__device__ __forceinline__ int last_le(const int *base, int n, int v) {     // largest i < n with base[i] <= v
+    int lo = 0, hi = n;
     while (hi - lo > 1) {
         const int mid = (lo + hi) >> 1;
-        if (tile_base[mid] <= mt) lo = mid; else hi = mid;
+        if (base[mid] <= v) lo = mid; else hi = mid;
     }
-    // experts without tiles share a base with their successor: step to the last one that starts at or before mt
-    t.u = lo;
-    t.e = ids[lo];
-    t.row0 = row_base[lo] + (mt - tile_base[lo]) * FG_BM;
-    t.cnt = min(FG_BM, row_base[lo + 1] - t.row0);
+    return lo;
+}
+__device__ __forceinline__ ItemInfo item_info(int item, int NB, int pairs_all, const int *pair_base, const int *single_base,
+                                              const int *row_base, const int *ids) {
+    ItemInfo t;
+    const int q = item / NB;
+    t.nb = item % NB;
+    int u, tile0;
+    if (q < pairs_all) {
+        u = last_le(pair_base, FG_MAXU, q);
+        tile0 = 2 * (q - pair_base[u]);
+        t.ntiles = 2;
+    } else {
+        u = last_le(single_base, FG_MAXU, q - pairs_all);
+        const int cnt = row_base[u + 1] - row_base[u];
+        tile0 = (cnt + FG_BM - 1) / FG_BM - 1;
+        t.ntiles = 1;
+    }
+    const int cnt = row_base[u + 1] - row_base[u];
+    t.e = ids[u];
+    t.row0 = row_base[u] + tile0 * FG_BM;
+    t.cnt0 = min(FG_BM, cnt - tile0 * FG_BM);
+    t.cnt1 = t.ntiles == 2 ? min(FG_BM, cnt - (tile0 + 1) * FG_BM) : 0;
     return t;
 }
 
 template <int MATS>
 struct FgCfg {
-    static constexpr int STAGES = MATS == 2 ? 3 : 6;
-    static constexpr int STAGE_BYTES = MATS == 2 ? 4 * FG_TILE_BYTES : 2 * FG_TILE_BYTES;   // A0 A1 B0 B1 | A0 B0
-    static constexpr int TMEM_COLS = MATS == 2 ? 512 : 256;                                  // 2 buffers of MATS x 128 columns
-    static constexpr size_t SMEM = 1024 /*align*/ + (size_t)STAGES * STAGE_BYTES + 8192 /*tables*/;
+    static constexpr int STAGES = MATS == 2 ? 3 : 4;
+    static constexpr int STAGE_BYTES = 3 * FG_TILE_BYTES;                                    // A tile 0, A tile 1, B
+    static constexpr int GBUF_BYTES = MATS == 2 ? 64 * 256 * 4 : 0;                          // silu(gate) as bf16 pairs
+    static constexpr int TABLE_BYTES = 256 + 3 * 128 * 4 + 2 * (FG_MAXU + 1) * 4 + 64;
+    static constexpr size_t SMEM = 1024 /*align*/ + (size_t)STAGES * STAGE_BYTES + GBUF_BYTES + TABLE_BYTES;
 };
 
 template <int MATS>
@@ -262,31 +294,35 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     extern __shared__ unsigned char smem_raw[];
     unsigned char *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-aligned operand tiles
     unsigned char *stages = smem;
-    unsigned char *tables = smem + (size_t)C::STAGES * C::STAGE_BYTES;
+    uint32_t *gbuf = reinterpret_cast<uint32_t *>(smem + (size_t)C::STAGES * C::STAGE_BYTES); // [64][256]
+    unsigned char *tables = smem + (size_t)C::STAGES * C::STAGE_BYTES + C::GBUF_BYTES;
     uint64_t *full = reinterpret_cast<uint64_t *>(tables);                 // [STAGES] A landed (tx) + 8 decode warps
     uint64_t *empty = full + C::STAGES;                                    // [STAGES] MMAs of the stage completed
-    uint64_t *tmem_full = empty + C::STAGES;                               // [2] accumulator complete
-    uint64_t *tmem_empty = tmem_full + 2;                                  // [2] accumulator drained (4 epilogue warps)
+    uint64_t *tmem_full = empty + C::STAGES;                               // [2] accumulators of a pass complete
+    uint64_t *tmem_empty = tmem_full + 2;                                  // [2] accumulators drained (8 epilogue warps)
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(tmem_empty + 2);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     float *scales = reinterpret_cast<float *>(tables + 256);               // [3][128]
-    int *tile_base = reinterpret_cast<int *>(tables + 256 + 3 * 128 * 4);  // [maxu + 1] (<= 1025 ints), then row_base
-    const int maxu = FG_MAXU;
-    int *row_base = nullptr;                                               // read from global (L1/L2 hits): keeps smem small
+    int *pair_base = reinterpret_cast<int *>(tables + 256 + 3 * 128 * 4);  // [FG_MAXU + 1]
+    int *single_base = pair_base + FG_MAXU + 1;                            // [FG_MAXU + 1]
+    const int *row_base = a.plan + PLAN_ROW_BASE;                          // global (L1 / L2 hits)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int KT = a.K >> 4, NTILES = a.N >> 4, NB = a.N >> 7, KS = a.K / FG_BK;
-    const int total = a.plan[0] * NB;
+    const int pairs_all = a.plan[2];
+    const int total = (pairs_all + a.plan[3]) * NB;
 
     if (tid == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(full + s, 9); mbar_init(empty + s, 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(tmem_full + b, 1); mbar_init(tmem_empty + b, 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(tmem_full + b, 1); mbar_init(tmem_empty + b, 8); }
         *abort_flag = 0;
         mbar_fence_init();
     }
-    for (int i = tid; i <= maxu; i += FG_THREADS) tile_base[i] = a.plan[PLAN_TILE_BASE + i];
-    row_base = const_cast<int *>(a.plan) + PLAN_ROW_BASE;
-    if (warp == 2) tmem_alloc(tmem_slot, C::TMEM_COLS);
+    for (int i = tid; i <= FG_MAXU; i += FG_THREADS) {
+        pair_base[i] = a.plan[PLAN_PAIR_BASE + i];
+        single_base[i] = a.plan[PLAN_SINGLE_BASE + i];
+    }
+    if (warp == 2) tmem_alloc(tmem_slot, 512);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -298,198 +334,217 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         if (warp == 0 && lane == 0) {
             uint32_t it = 0;
             for (int item = blockIdx.x; item < total && !*abort_flag; item += gridDim.x) {
-                const TileInfo t = tile_info(item, NB, tile_base, row_base, a.ids, maxu);
-                for (int s = 0; s < KS; ++s, ++it) {
-                    const int slot = it % C::STAGES;
-                    const uint32_t n = it / C::STAGES;
-                    if (!wait_or_abort(empty + slot, (n & 1) ^ 1, abort_flag, a.status, GF_STATUS_TMA_TIMEOUT)) break;
-                    unsigned char *st = stages + (size_t)slot * C::STAGE_BYTES;
-                    const bool two = MATS == 2 && !a.shared_x;
-                    mbar_expect_tx(full + slot, (two ? 2 : 1) * FG_TILE_BYTES);
-                    tma_load_2d(st, &mapA0, s * FG_BK, t.row0, full + slot);
-                    if (two) tma_load_2d(st + FG_TILE_BYTES, &mapA1, s * FG_BK, t.row0, full + slot);
-                }
-            }
-        } else if (warp == 1 && lane == 0) {
-            uint32_t it = 0, ti = 0;
-            for (int item = blockIdx.x; item < total && !*abort_flag; item += gridDim.x, ++ti) {
-                const uint32_t buf = ti & 1;
-                if (!wait_or_abort(tmem_empty + buf, ((ti >> 1) & 1) ^ 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) break;
-                tc_fence_after();
-                const uint32_t d0 = tmem_base + buf * (MATS * FG_BN);
+                const ItemInfo t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
                 bool ok = true;
-                for (int s = 0; s < KS; ++s, ++it) {
-                    const int slot = it % C::STAGES;
-                    const uint32_t n = it / C::STAGES;
-                    if (!wait_or_abort(full + slot, n & 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) { ok = false; break; }
-                    tc_fence_after();
-                    const uint32_t sa = smem_u32(stages + (size_t)slot * C::STAGE_BYTES);
-                    const uint32_t a0 = sa, a1 = (MATS == 2 && !a.shared_x) ? sa + FG_TILE_BYTES : sa;
-                    const uint32_t b0 = sa + (MATS == 2 ? 2 : 1) * FG_TILE_BYTES, b1 = b0 + FG_TILE_BYTES;
-#pragma unroll
-                    for (int kk = 0; kk < FG_BK / 16; ++kk) {
-                        const uint32_t acc = (s > 0 || kk > 0) ? 1u : 0u;
-                        umma_f16(d0, umma_desc_sw128(a0 + kk * 32), umma_desc_sw128(b0 + kk * 32), UMMA_IDESC, acc);
-                        if (MATS == 2)
-                            umma_f16(d0 + FG_BN, umma_desc_sw128(a1 + kk * 32), umma_desc_sw128(b1 + kk * 32), UMMA_IDESC, acc);
+                for (int pm = 0; pm < MATS && ok; ++pm) {
+                    const CUtensorMap *map = (pm == 1 && !a.shared_x) ? &mapA1 : &mapA0;
+                    for (int s = 0; s < KS; ++s, ++it) {
+                        const int slot = it % C::STAGES;
+                        const uint32_t n = it / C::STAGES;
+                        if (!wait_or_abort(empty + slot, (n & 1) ^ 1, abort_flag, a.status, GF_STATUS_TMA_TIMEOUT)) { ok = false; break; }
+                        unsigned char *st = stages + (size_t)slot * C::STAGE_BYTES;
+                        mbar_expect_tx(full + slot, t.ntiles * FG_TILE_BYTES);
+                        tma_load_2d(st, map, s * FG_BK, t.row0, full + slot);
+                        if (t.ntiles == 2) tma_load_2d(st + FG_TILE_BYTES, map, s * FG_BK, t.row0 + FG_BM, full + slot);
                     }
-                    umma_commit(empty + slot);              // the stage may be overwritten once these MMAs have read it
                 }
                 if (!ok) break;
-                umma_commit(tmem_full + buf);               // the accumulators of this item are complete
+            }
+        } else if (warp == 1 && lane == 0) {
+            uint32_t it = 0, pc = 0;
+            for (int item = blockIdx.x; item < total && !*abort_flag; item += gridDim.x) {
+                const ItemInfo t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
+                bool ok = true;
+                for (int pm = 0; pm < MATS && ok; ++pm, ++pc) {
+                    const uint32_t pb = pc & 1;
+                    if (!wait_or_abort(tmem_empty + pb, ((pc >> 1) & 1) ^ 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t d0 = tmem_base + pb * 256;
+                    for (int s = 0; s < KS; ++s, ++it) {
+                        const int slot = it % C::STAGES;
+                        const uint32_t n = it / C::STAGES;
+                        if (!wait_or_abort(full + slot, n & 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) { ok = false; break; }
+                        tc_fence_after();
+                        const uint32_t sa = smem_u32(stages + (size_t)slot * C::STAGE_BYTES);
+                        const uint32_t sb = sa + 2 * FG_TILE_BYTES;
+#pragma unroll
+                        for (int kk = 0; kk < FG_BK / 16; ++kk) {
+                            const uint32_t acc = (s > 0 || kk > 0) ? 1u : 0u;
+                            const uint64_t bd = umma_desc_sw128(sb + kk * 32);
+                            umma_f16(d0, umma_desc_sw128(sa + kk * 32), bd, UMMA_IDESC, acc);
+                            if (t.ntiles == 2) umma_f16(d0 + FG_BN, umma_desc_sw128(sa + FG_TILE_BYTES + kk * 32), bd, UMMA_IDESC, acc);
+                        }
+                        umma_commit(empty + slot);          // the stage may be overwritten once these MMAs have read it
+                    }
+                    if (ok) umma_commit(tmem_full + pb);    // the accumulators of this pass are complete
+                }
+                if (!ok) break;
             }
         }
-    } else if (warp < 8) {
-        // ------------------------------------------------------------------ warpgroup 1: epilogue
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;");
-        const int q = warp & 3, m = q * 32 + lane;           // TMEM lane == row of the M tile
-        uint32_t ti = 0;
-        for (int item = blockIdx.x; item < total; item += gridDim.x, ++ti) {
-            const TileInfo t = tile_info(item, NB, tile_base, row_base, a.ids, maxu);
-            const uint32_t buf = ti & 1;
-            // scale vectors of (expert, column block): one element per thread, shared by the 128 epilogue threads
-            asm volatile("bar.sync 1, 128;");
-            {
-                const size_t o = (size_t)t.e * a.N + t.nb * 128 + m;
-                scales[m] = __half2float(a.sv0[o]);
-                if (MATS == 2) { scales[128 + m] = __half2float(a.sv1[o]); scales[256 + m] = __half2float(a.sd[o]); }
+    } else if (warp < 12) {
+        // ------------------------------------------------------------------ warpgroups 1-2: epilogue (tile 0 | tile 1)
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+        const int q = warp & 3, tl = (warp - 4) >> 2;        // TMEM lane quadrant, M tile of the item
+        const int m = q * 32 + lane, em = tl * 128 + m;      // row of the tile, row of the item (0..255)
+        uint32_t pc = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+            const ItemInfo t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
+            const bool has = tl < t.ntiles;
+            const int cnt = tl == 0 ? t.cnt0 : t.cnt1;
+            // scale vectors of (expert, column block): written by the first 128 epilogue threads, read by all 256
+            asm volatile("bar.sync 1, 256;");
+            if (em < 128) {
+                const size_t o = (size_t)t.e * a.N + t.nb * 128 + em;
+                scales[em] = __half2float(a.sv0[o]);
+                if (MATS == 2) { scales[128 + em] = __half2float(a.sv1[o]); scales[256 + em] = __half2float(a.sd[o]); }
             }
-            asm volatile("bar.sync 1, 128;");
-            if (!wait_or_abort(tmem_full + buf, (ti >> 1) & 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) break;
-            tc_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + buf * (MATS * FG_BN);
+            asm volatile("bar.sync 1, 256;");
             float v[128];
+            for (int pm = 0; pm < MATS; ++pm, ++pc) {
+                const uint32_t pb = pc & 1;
+                if (!wait_or_abort(tmem_full + pb, (pc >> 1) & 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) { ok = false; break; }
+                tc_fence_after();
+                if (has) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + pb * 256 + tl * FG_BN;
 #pragma unroll
-            for (int c = 0; c < 4; ++c) tmem_ld32(taddr + c * 32, v + c * 32);
-            tmem_ld_wait();
-            if (MATS == 2) {
-                uint32_t gpk[64];                            // gate after scale / bf16 rounding / clamp, two per register
-                fwht128_regs(v);
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const float g0 = fminf(bf16r(v[2 * i] * HAD_SCALE * scales[2 * i]), a.limit);
-                    const float g1 = fminf(bf16r(v[2 * i + 1] * HAD_SCALE * scales[2 * i + 1]), a.limit);
-                    gpk[i] = (__float_as_uint(g0) >> 16) | (__float_as_uint(g1) & 0xffff0000u);
+                    for (int c = 0; c < 4; ++c) tmem_ld32(taddr + c * 32, v + c * 32);
+                    tmem_ld_wait();
                 }
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(taddr + FG_BN + c * 32, v + c * 32);
-                tmem_ld_wait();
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty + buf);            // both accumulators are in registers
+                if (lane == 0) mbar_arrive(tmem_empty + pb);             // this warp's rows are in registers
+                if (!has) continue;
                 fwht128_regs(v);
+                if (MATS == 2 && pm == 0) {
+                    // gate: scale, bf16 rounding, clamp, silu (rounded) -> two bf16 per word, this thread's column of gbuf
 #pragma unroll
-                for (int i = 0; i < 128; ++i) {
-                    const float gg = __uint_as_float((i & 1) ? (gpk[i >> 1] & 0xffff0000u) : (gpk[i >> 1] << 16));
-                    const float uu = fminf(fmaxf(bf16r(v[i] * HAD_SCALE * scales[128 + i]), -a.limit), a.limit);
-                    const float act = bf16r(bf16r(gg / (1.f + expf(-gg))) * uu);
-                    v[i] = act * scales[256 + i];
-                }
-                fwht128_regs(v);
-                if (m < t.cnt) {
-                    uint4 *o = reinterpret_cast<uint4 *>(a.xd + (size_t)(t.row0 + m) * a.N + t.nb * 128);
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        __half2 h[4];
-#pragma unroll
-                        for (int j = 0; j < 4; ++j)
-                            h[j] = __halves2half2(__float2half_rn(v[8 * c + 2 * j] * HAD_SCALE),
-                                                  __float2half_rn(v[8 * c + 2 * j + 1] * HAD_SCALE));
-                        o[c] = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
-                                          *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
+                    for (int i = 0; i < 64; ++i) {
+                        const float g0 = fminf(bf16r(v[2 * i] * HAD_SCALE * scales[2 * i]), a.limit);
+                        const float g1 = fminf(bf16r(v[2 * i + 1] * HAD_SCALE * scales[2 * i + 1]), a.limit);
+                        const float s0 = bf16r(__fdividef(g0, 1.f + __expf(-g0)));
+                        const float s1 = bf16r(__fdividef(g1, 1.f + __expf(-g1)));
+                        gbuf[i * 256 + em] = (__float_as_uint(s0) >> 16) | (__float_as_uint(s1) & 0xffff0000u);
                     }
-                }
-            } else {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(tmem_empty + buf);
-                fwht128_regs(v);
-                if (m < t.cnt) {
-                    const int p = a.src_pair[t.row0 + m];
-                    float4 *o = reinterpret_cast<float4 *>(a.y + (size_t)p * a.N + t.nb * 128);
+                } else if (MATS == 2) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c)
-                        o[c] = make_float4(v[4 * c] * HAD_SCALE * scales[4 * c], v[4 * c + 1] * HAD_SCALE * scales[4 * c + 1],
-                                           v[4 * c + 2] * HAD_SCALE * scales[4 * c + 2], v[4 * c + 3] * HAD_SCALE * scales[4 * c + 3]);
+                    for (int i = 0; i < 64; ++i) {
+                        const uint32_t gp = gbuf[i * 256 + em];
+                        const float u0 = fminf(fmaxf(bf16r(v[2 * i] * HAD_SCALE * scales[128 + 2 * i]), -a.limit), a.limit);
+                        const float u1 = fminf(fmaxf(bf16r(v[2 * i + 1] * HAD_SCALE * scales[128 + 2 * i + 1]), -a.limit), a.limit);
+                        v[2 * i] = bf16r(__uint_as_float(gp << 16) * u0) * scales[256 + 2 * i];
+                        v[2 * i + 1] = bf16r(__uint_as_float(gp & 0xffff0000u) * u1) * scales[256 + 2 * i + 1];
+                    }
+                    fwht128_regs(v);
+                    if (m < cnt) {
+                        uint4 *o = reinterpret_cast<uint4 *>(a.xd + (size_t)(t.row0 + em) * a.N + t.nb * 128);
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            __half2 h[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                h[j] = __halves2half2(__float2half_rn(v[8 * c + 2 * j] * HAD_SCALE),
+                                                      __float2half_rn(v[8 * c + 2 * j + 1] * HAD_SCALE));
+                            o[c] = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
+                                              *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
+                        }
+                    }
+                } else {
+                    if (m < cnt) {
+                        const int p = a.src_pair[t.row0 + em];
+                        float4 *o = reinterpret_cast<float4 *>(a.y + (size_t)p * a.N + t.nb * 128);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c)
+                            o[c] = make_float4(v[4 * c] * HAD_SCALE * scales[4 * c], v[4 * c + 1] * HAD_SCALE * scales[4 * c + 1],
+                                               v[4 * c + 2] * HAD_SCALE * scales[4 * c + 2], v[4 * c + 3] * HAD_SCALE * scales[4 * c + 3]);
+                    }
                 }
             }
         }
     } else {
-        // ------------------------------------------------------------------ warpgroups 2-3: trellis decode of B
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
-        const int dw = warp - 8;
-        constexpr int NTL = MATS == 2 ? 8 : 4;               // n tiles of this warp per stage
-        const int mat = MATS == 2 ? (dw >> 2) : 0;
-        const int ktl = dw & 3;
-        const int nt_begin = MATS == 2 ? 0 : (dw >> 2) * 4;
+        // ------------------------------------------------------------------ warpgroups 3-4: trellis decode of B
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+        const int dw = warp - 12;
+        constexpr int NTL = 4;                               // n tiles of this warp per stage
+        const int ktl = dw & 3, nt_begin = (dw >> 2) * 4;
         const int g = lane >> 2, tq = lane & 3;
-        const uint32_t *Tm = mat ? a.T1 : a.T0;
-        // byte offsets inside a B tile of this lane's four 32-bit stores (before the n-tile offset)
+        // byte offsets inside the B tile of this lane's four 32-bit stores (before the n-tile offset)
         const int c0 = 2 * ktl, c1 = 2 * ktl + 1;
-        const int off_lo0 = g * 128 + ((c0 ^ g) << 4) + 4 * tq;            // n = g,     k = 2t
-        const int off_lo1 = g * 128 + ((c1 ^ g) << 4) + 4 * tq;            // n = g,     k = 2t + 8
-        const int off_hi0 = off_lo0 + 8 * 128, off_hi1 = off_lo1 + 8 * 128; // n = g + 8 (same n & 7)
+        const int off_lo0 = nt_begin * 2048 + g * 128 + ((c0 ^ g) << 4) + 4 * tq;     // n = g,     k = 2t
+        const int off_lo1 = nt_begin * 2048 + g * 128 + ((c1 ^ g) << 4) + 4 * tq;     // n = g,     k = 2t + 8
         uint32_t it = 0;
-        uint32_t wcur[NTL], wnext[NTL];
-        int item = blockIdx.x;
-        auto load_words = [&](const TileInfo &t, int s, uint32_t (&w)[NTL]) {
-            const uint32_t *src = Tm + (((size_t)t.e * KT + 4 * s + ktl) * NTILES + (size_t)t.nb * 8 + nt_begin) * 32 + lane;
+        bool ok = true;
+        int item = blockIdx.x, pm = 0;
+        ItemInfo t{};
+        auto src_of = [&](const ItemInfo &ti, int pmat, int s) {
+            return (pmat ? a.T1 : a.T0) + (((size_t)ti.e * KT + 4 * s + ktl) * NTILES + (size_t)ti.nb * 8 + nt_begin) * 32 + lane;
+        };
+        auto load_words = [&](const uint32_t *src, uint32_t (&w)[NTL]) {
 #pragma unroll
             for (int i = 0; i < NTL; ++i) w[i] = __ldg(src + i * 32);
         };
-        TileInfo t{};
-        if (item < total) {
-            t = tile_info(item, NB, tile_base, row_base, a.ids, maxu);
-            load_words(t, 0, wcur);
-        }
-        while (item < total && !*abort_flag) {
-            const int next_item = item + gridDim.x;
-            TileInfo tn{};
-            if (next_item < total) tn = tile_info(next_item, NB, tile_base, row_base, a.ids, maxu);
-            bool ok = true;
-            for (int s = 0; s < KS; ++s, ++it) {
-                if (s + 1 < KS) load_words(t, s + 1, wnext);
-                else if (next_item < total) load_words(tn, 0, wnext);
-                const int slot = it % C::STAGES;
-                const uint32_t n = it / C::STAGES;
-                if (!wait_or_abort(empty + slot, (n & 1) ^ 1, abort_flag, a.status, GF_STATUS_TMA_TIMEOUT)) { ok = false; break; }
-                unsigned char *bt = stages + (size_t)slot * C::STAGE_BYTES + (MATS == 2 ? 2 + mat : 1) * FG_TILE_BYTES +
-                                    nt_begin * 16 * 128;
+        auto do_stage = [&](const uint32_t (&wr)[NTL]) {
+            const int slot = it % C::STAGES;
+            const uint32_t n = it / C::STAGES;
+            if (!wait_or_abort(empty + slot, (n & 1) ^ 1, abort_flag, a.status, GF_STATUS_TMA_TIMEOUT)) { ok = false; return; }
+            unsigned char *bt = stages + (size_t)slot * C::STAGE_BYTES + 2 * FG_TILE_BYTES;
 #pragma unroll
-                for (int i = 0; i < NTL; ++i) {
-                    const uint32_t w = wcur[i];
-                    const uint32_t pw = __shfl_sync(0xffffffffu, w, (lane + 31) & 31);
-                    uint32_t x0, x1, x2, x3, x4, x5, x6, x7;
-                    codeword_pair(__funnelshift_r(w, pw, 12), x0, x4);     // j = 0 | 4
-                    codeword_pair(__funnelshift_r(w, pw, 8), x1, x5);      // j = 1 | 5
-                    codeword_pair(__funnelshift_r(w, pw, 4), x2, x6);      // j = 2 | 6
-                    codeword_pair(w, x3, x7);                              // j = 3 | 7
-                    const uint32_t p01 = __byte_perm(weight_dup(x0), weight_dup(x1), 0x5410);
-                    const uint32_t p23 = __byte_perm(weight_dup(x2), weight_dup(x3), 0x5410);
-                    const uint32_t p45 = __byte_perm(weight_dup(x4), weight_dup(x5), 0x5410);
-                    const uint32_t p67 = __byte_perm(weight_dup(x6), weight_dup(x7), 0x5410);
-                    unsigned char *tb = bt + i * 16 * 128;
-                    *reinterpret_cast<uint32_t *>(tb + off_lo0) = p01;
-                    *reinterpret_cast<uint32_t *>(tb + off_lo1) = p23;
-                    *reinterpret_cast<uint32_t *>(tb + off_hi0) = p45;
-                    *reinterpret_cast<uint32_t *>(tb + off_hi1) = p67;
-                }
-                fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
-                __syncwarp();
-                if (lane == 0) mbar_arrive(full + slot);
-#pragma unroll
-                for (int i = 0; i < NTL; ++i) wcur[i] = wnext[i];
+            for (int i = 0; i < NTL; ++i) {
+                const uint32_t w = wr[i];
+                const uint32_t pw = __shfl_sync(0xffffffffu, w, (lane + 31) & 31);
+                uint32_t x0, x1, x2, x3, x4, x5, x6, x7;
+                codeword_pair(__funnelshift_r(w, pw, 12), x0, x4);     // j = 0 | 4
+                codeword_pair(__funnelshift_r(w, pw, 8), x1, x5);      // j = 1 | 5
+                codeword_pair(__funnelshift_r(w, pw, 4), x2, x6);      // j = 2 | 6
+                codeword_pair(w, x3, x7);                              // j = 3 | 7
+                const uint32_t p01 = __byte_perm(weight_dup(x0), weight_dup(x1), 0x5410);
+                const uint32_t p23 = __byte_perm(weight_dup(x2), weight_dup(x3), 0x5410);
+                const uint32_t p45 = __byte_perm(weight_dup(x4), weight_dup(x5), 0x5410);
+                const uint32_t p67 = __byte_perm(weight_dup(x6), weight_dup(x7), 0x5410);
+                unsigned char *tb = bt + i * 2048;
+                *reinterpret_cast<uint32_t *>(tb + off_lo0) = p01;
+                *reinterpret_cast<uint32_t *>(tb + off_lo1) = p23;
+                *reinterpret_cast<uint32_t *>(tb + off_lo0 + 1024) = p45;           // n = g + 8
+                *reinterpret_cast<uint32_t *>(tb + off_lo1 + 1024) = p67;
             }
-            if (!ok) break;
-            item = next_item;
-            t = tn;
+            fence_async_smem();                              // generic-proxy stores -> visible to the tensor core
+            __syncwarp();
+            if (lane == 0) mbar_arrive(full + slot);
+            ++it;
+        };
+        uint32_t w0[NTL], w1[NTL];
+        bool valid = item < total;
+        if (valid) {
+            t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
+            load_words(src_of(t, 0, 0), w0);
+        }
+        while (valid && ok && !*abort_flag) {
+            // the pass after this one: the item's second matrix, or the first matrix of the CTA's next item
+            int n_item = item, n_pm = pm + 1;
+            ItemInfo tn = t;
+            bool n_valid = true;
+            if (n_pm == MATS) {
+                n_pm = 0;
+                n_item = item + gridDim.x;
+                n_valid = n_item < total;
+                if (n_valid) tn = item_info(n_item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
+            }
+            for (int s = 0; s < KS && ok; s += 2) {          // KS is even: stage parity == register buffer
+                load_words(src_of(t, pm, s + 1), w1);
+                do_stage(w0);
+                if (!ok) break;
+                if (s + 2 < KS) load_words(src_of(t, pm, s + 2), w0);
+                else if (n_valid) load_words(src_of(tn, n_pm, 0), w0);
+                do_stage(w1);
+            }
+            item = n_item; pm = n_pm; t = tn; valid = n_valid;
         }
     }
 
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    if (warp == 2) tmem_dealloc(tmem_base, C::TMEM_COLS);
+    if (warp == 2) tmem_dealloc(tmem_base, 512);
 }
 
 }  // namespace gf
