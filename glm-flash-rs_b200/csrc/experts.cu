@@ -138,6 +138,42 @@ extern "C" int glmflash_experts_run_rows(glmflash_experts *e, void *stream, cons
     return launch_gemv(s, 1, a, umax, pdl);
 }
 
+// The layer pipeline's form of run_rows (used by Moe for windows of <= 16 rows): no grouping tables and no rotation
+// kernel -- the gate/up kernel derives expert and members from the routing table and rotates the input itself, the
+// down kernel derives them again.  Two launches instead of four; the arithmetic per pair is that of run_rows.
+namespace gf {
+int experts_run_fused(glmflash_experts *e, cudaStream_t s, const glmflash_weights *w, const void *input, int x_stride,
+                      const int32_t *picks, int rows) {
+    const glmflash_config &c = e->cfg;
+    GF_REQUIRE(rows > 0 && rows <= c.max_rows, "expert verifier row/member bounds");
+    GF_REQUIRE(x_stride >= c.hidden && x_stride % 4 == 0, "x_stride must be >= hidden and a multiple of 4");
+    GF_REQUIRE(((uintptr_t)w->gt | (uintptr_t)w->ut | (uintptr_t)w->dt) % 16 == 0, "trellis tensors must be 16-byte aligned");
+    GF_REQUIRE(((uintptr_t)input | (uintptr_t)w->suh_g | (uintptr_t)w->suh_u) % 8 == 0, "input and scale vectors must be 8-byte aligned");
+    const bool pdl = c.pdl != 0;
+    const int H = c.hidden, I = c.inter, P = rows * c.slots, E1 = c.experts + 1;
+    const int umax = std::min(rows * (c.slots - 1) + 1, E1);
+    GemvArgs a{};
+    a.status = e->status;
+    a.P = P; a.maxm = rows; a.slots = c.slots; a.E = c.experts; a.e_lo = c.expert_lo; a.e_hi = c.expert_hi;
+    a.shared_exl3 = c.shared_exl3; a.limit = c.limit;
+    a.picks = picks; a.rows = rows;
+    // gate + up on the rotated input, SwiGLU, down-input rotation -> xd
+    a.xin = (const __nv_bfloat16 *)input; a.x_stride = x_stride; a.wait_first = 1;
+    a.suh0 = (const __half *)w->suh_g; a.suh1 = (const __half *)w->suh_u;
+    a.T0 = w->gt; a.T1 = w->ut;
+    a.sv0 = (const __half *)w->svh_g; a.sv1 = (const __half *)w->svh_u; a.sd = (const __half *)w->suh_d;
+    a.xd = e->xd; a.y = nullptr; a.K = H; a.N = I; a.mode = GEMV_GATEUP;
+    if ((e->phases & 2) && launch_gemv(s, 2, a, umax, pdl)) return -1;
+    if (!(e->phases & 4)) return 0;
+    // down -> y (the routing table was consumed by the kernel before: it may be read before the dependency wait)
+    a.xin = nullptr; a.wait_first = 0; a.suh0 = a.suh1 = nullptr;
+    a.X0 = e->xd; a.X1 = e->xd; a.T0 = w->dt; a.T1 = w->dt;
+    a.sv0 = (const __half *)w->svh_d; a.sv1 = nullptr; a.sd = nullptr;
+    a.xd = nullptr; a.y = e->y; a.K = I; a.N = H; a.mode = GEMV_DOWN;
+    return launch_gemv(s, 1, a, umax, pdl);
+}
+}  // namespace gf
+
 extern "C" int glmflash_experts_set_phases(glmflash_experts *e, int mask) {
     GF_REQUIRE(e != nullptr, "null argument");
     e->phases = mask;

@@ -56,6 +56,8 @@ constexpr int PLAN_PAIR_BASE = 4, PLAN_SINGLE_BASE = PLAN_PAIR_BASE + FG_MAXU + 
               PLAN_ROW_BASE = PLAN_SINGLE_BASE + FG_MAXU + 1, PLAN_INTS = PLAN_ROW_BASE + FG_MAXU + 1;
 
 // ---------------------------------------------------------------------------------------------- plan
+// Launched with one block per bank entry: every block recomputes the (tiny) scans, block 0 publishes the plan,
+// block b writes the grouped rows of distinct expert b.
 __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restrict__ ids, const int *__restrict__ count,
                                                           const int *__restrict__ members, int maxm, int slots, int E,
                                                           int shared_exl3, int e_lo, int e_hi, int *__restrict__ plan,
@@ -96,17 +98,19 @@ __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restric
     }
     const int p_ex = p_off + p_inc - pairs, s_ex = s_off + s_inc - single, r_ex = r_off + r_inc - cnt;
     cnt_sh[u] = cnt; row_sh[u] = r_ex; e_sh[u] = e;
-    plan[PLAN_PAIR_BASE + u] = p_ex;
-    plan[PLAN_SINGLE_BASE + u] = s_ex;
-    plan[PLAN_ROW_BASE + u] = r_ex;
-    if (u == 0) {
+    if (blockIdx.x == 0) {
+        plan[PLAN_PAIR_BASE + u] = p_ex;
+        plan[PLAN_SINGLE_BASE + u] = s_ex;
+        plan[PLAN_ROW_BASE + u] = r_ex;
+    }
+    if (u == 0 && blockIdx.x == 0) {
         plan[0] = t_all; plan[1] = r_all; plan[2] = p_all; plan[3] = s_all;
         plan[PLAN_PAIR_BASE + FG_MAXU] = p_all;
         plan[PLAN_SINGLE_BASE + FG_MAXU] = s_all;
         plan[PLAN_ROW_BASE + FG_MAXU] = r_all;
     }
     __syncthreads();
-    for (int uu = 0; uu < n; ++uu) {
+    for (int uu = blockIdx.x; uu < n; uu += gridDim.x) {
         const int c = cnt_sh[uu], rb = row_sh[uu], ee = e_sh[uu];
         for (int m = u; m < c; m += FG_MAXU) {
             const int code = members[(size_t)uu * maxm + m];
@@ -117,7 +121,8 @@ __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restric
 }
 
 // ---------------------------------------------------------------------------------------------- rotation
-// One warp per (grouped row, 128-block, matrix).
+// One CTA (8 warps) per grouped row: the row's expert and source row are looked up once, every warp rotates
+// K/128/8 blocks, for one (shared_x) or both input scale vectors.
 __global__ void __launch_bounds__(256) fast_rot_kernel(const __nv_bfloat16 *__restrict__ x, int x_stride,
                                                        const int *__restrict__ plan, const int *__restrict__ src_pair,
                                                        const int *__restrict__ row_expert, const __half *__restrict__ suh0,
@@ -125,21 +130,26 @@ __global__ void __launch_bounds__(256) fast_rot_kernel(const __nv_bfloat16 *__re
                                                        __half *__restrict__ out1, int K, int slots, int mats) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int KB = K >> 7, rows = plan[1];
-    const long item = (long)blockIdx.x * 8 + warp;
-    if (item >= (long)rows * KB * mats) return;
-    const int blk = (int)(item % KB);
-    const int j = (int)((item / KB) % rows), mat = (int)(item / ((long)KB * rows));
-    const int p = src_pair[j], e = row_expert[j], row = p / slots;
-    const __half *suh = (mat ? suh1 : suh0) + (size_t)e * K + blk * 128 + 4 * lane;
-    const __nv_bfloat16 *xr = x + (size_t)row * x_stride + blk * 128 + 4 * lane;
-    float v[4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = __bfloat162float(xr[i]) * __half2float(suh[i]);
-    fwht128(v, lane);
-    __half *o = (mat ? out1 : out0) + (size_t)j * K + blk * 128 + 4 * lane;
-    __half2 h01 = __halves2half2(__float2half_rn(v[0] * HAD_SCALE), __float2half_rn(v[1] * HAD_SCALE));
-    __half2 h23 = __halves2half2(__float2half_rn(v[2] * HAD_SCALE), __float2half_rn(v[3] * HAD_SCALE));
-    *reinterpret_cast<uint2 *>(o) = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+    for (int j = blockIdx.x; j < rows; j += gridDim.x) {
+        const int p = src_pair[j], e = row_expert[j], row = p / slots;
+        for (int blk = warp; blk < KB; blk += 8) {
+            const int k = blk * 128 + 4 * lane;
+            const uint2 xv = *reinterpret_cast<const uint2 *>(x + (size_t)row * x_stride + k);
+            const __nv_bfloat162 x01 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.x),
+                                 x23 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.y);
+            const float xf[4] = {__bfloat162float(x01.x), __bfloat162float(x01.y), __bfloat162float(x23.x), __bfloat162float(x23.y)};
+            for (int mat = 0; mat < mats; ++mat) {
+                const uint2 sv = *reinterpret_cast<const uint2 *>((mat ? suh1 : suh0) + (size_t)e * K + k);
+                const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv.x), s23 = *reinterpret_cast<const __half2 *>(&sv.y);
+                float v[4] = {xf[0] * __low2float(s01), xf[1] * __high2float(s01), xf[2] * __low2float(s23), xf[3] * __high2float(s23)};
+                fwht128(v, lane);
+                __half2 h01 = __halves2half2(__float2half_rn(v[0] * HAD_SCALE), __float2half_rn(v[1] * HAD_SCALE));
+                __half2 h23 = __halves2half2(__float2half_rn(v[2] * HAD_SCALE), __float2half_rn(v[3] * HAD_SCALE));
+                *reinterpret_cast<uint2 *>((mat ? out1 : out0) + (size_t)j * K + k) =
+                    make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+            }
+        }
+    }
 }
 
 // ---------------------------------------------------------------------------------------------- tcgen05 helpers
@@ -207,9 +217,10 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
 
 // Wait on an mbarrier phase, giving up when the abort flag is up or after a bounded number of polls.
 __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, volatile int *abort_flag, int *status, int code) {
-    for (uint32_t i = 0; i < 20000000u; ++i) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 63u) == 63u && *abort_flag) return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < 400000u; ++i) {                  // each poll may sleep up to 10 us: at most about 4 s
+        if (mbar_try_wait_hint(bar, parity, 10000u)) return true;
+        if (*abort_flag) return false;
     }
     *abort_flag = 1;
     atomicExch(status, code);
@@ -512,32 +523,40 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             if (lane == 0) mbar_arrive(full + slot);
             ++it;
         };
-        uint32_t w0[NTL], w1[NTL];
+        // Packed words are fetched three stages ahead into four register buffers; KS is a multiple of 4, so the
+        // buffer of a stage is s & 3 at compile time.  (pass, stage) + d stages ahead, across pass / item boundaries:
+        uint32_t w0[NTL], w1[NTL], w2[NTL], w3[NTL];
         bool valid = item < total;
-        if (valid) {
-            t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
-            load_words(src_of(t, 0, 0), w0);
-        }
-        while (valid && ok && !*abort_flag) {
-            // the pass after this one: the item's second matrix, or the first matrix of the CTA's next item
-            int n_item = item, n_pm = pm + 1;
-            ItemInfo tn = t;
-            bool n_valid = true;
+        int n_item = item, n_pm = 0;
+        ItemInfo tn{};
+        bool n_valid = false;
+        auto fetch = [&](int s, uint32_t (&w)[NTL]) {          // stage s of the current pass; s >= KS: the next pass
+            if (s < KS) load_words(src_of(t, pm, s), w);
+            else if (n_valid) load_words(src_of(tn, n_pm, s - KS), w);
+        };
+        auto advance = [&]() {                                 // describe the pass after (item, pm)
+            n_item = item; n_pm = pm + 1; tn = t; n_valid = true;
             if (n_pm == MATS) {
                 n_pm = 0;
                 n_item = item + gridDim.x;
                 n_valid = n_item < total;
                 if (n_valid) tn = item_info(n_item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
             }
-            for (int s = 0; s < KS && ok; s += 2) {          // KS is even: stage parity == register buffer
-                load_words(src_of(t, pm, s + 1), w1);
-                do_stage(w0);
-                if (!ok) break;
-                if (s + 2 < KS) load_words(src_of(t, pm, s + 2), w0);
-                else if (n_valid) load_words(src_of(tn, n_pm, 0), w0);
-                do_stage(w1);
+        };
+        if (valid) {
+            t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
+            advance();
+            fetch(0, w0); fetch(1, w1); fetch(2, w2);
+        }
+        while (valid && ok && !*abort_flag) {
+            for (int s = 0; s < KS && ok; s += 4) {
+                fetch(s + 3, w3); do_stage(w0); if (!ok) break;
+                fetch(s + 4, w0); do_stage(w1); if (!ok) break;
+                fetch(s + 5, w1); do_stage(w2); if (!ok) break;
+                fetch(s + 6, w2); do_stage(w3);
             }
             item = n_item; pm = n_pm; t = tn; valid = n_valid;
+            if (valid) advance();
         }
     }
 
@@ -642,17 +661,17 @@ extern "C" int glmflash_fast_experts_run(glmflash_fast_experts *f, void *stream,
     GF_REQUIRE(rows > 0 && rows <= c.max_rows && maxm >= rows && maxm <= c.max_rows, "expert rows/member stride outside scratch");
     GF_REQUIRE(x_stride >= c.hidden && x_stride % 4 == 0, "x_stride must be >= hidden and a multiple of 4");
     GF_REQUIRE(((uintptr_t)w->gt | (uintptr_t)w->ut | (uintptr_t)w->dt) % 16 == 0, "trellis tensors must be 16-byte aligned");
+    GF_REQUIRE(((uintptr_t)input | (uintptr_t)w->suh_g | (uintptr_t)w->suh_u) % 8 == 0, "input and scale vectors must be 8-byte aligned");
     cudaStream_t s = (cudaStream_t)stream;
     const int H = c.hidden, I = c.inter;
     const long P = (long)rows * c.slots;
     if (f->phases & 1)
-        fast_plan_kernel<<<1, FG_MAXU, 0, s>>>(ids, count, members, maxm, c.slots, c.experts, c.shared_exl3, c.expert_lo,
+        fast_plan_kernel<<<c.experts + 1, FG_MAXU, 0, s>>>(ids, count, members, maxm, c.slots, c.experts, c.shared_exl3, c.expert_lo,
                                               c.expert_hi, f->plan, f->src_pair, f->row_expert);
     GF_CUDA(cudaGetLastError());
     const int mats = shared_x ? 1 : 2;
-    const long items = P * (H / 128) * mats;
     if (f->phases & 2)
-        fast_rot_kernel<<<(unsigned)((items + 7) / 8), 256, 0, s>>>((const __nv_bfloat16 *)input, x_stride, f->plan, f->src_pair,
+        fast_rot_kernel<<<(unsigned)std::min<long>(P, 148L * 32), 256, 0, s>>>((const __nv_bfloat16 *)input, x_stride, f->plan, f->src_pair,
                                                               f->row_expert, (const __half *)w->suh_g, (const __half *)w->suh_u,
                                                               f->xg, f->xu, H, c.slots, mats);
     GF_CUDA(cudaGetLastError());

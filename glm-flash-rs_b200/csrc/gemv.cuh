@@ -52,6 +52,13 @@ struct GemvArgs {
     int *status;
     int K, N, P, SK, KTC, maxm, slots, E, e_lo, e_hi, shared_exl3, mode;
     float limit;
+    // fused front end (the layer pipeline of windows of <= 16 rows): with picks != nullptr the CTA derives its expert
+    // and members from the routing table itself (no grouping kernel), with xin != nullptr it rotates the layer input
+    // itself (no rotation kernel, no Xg / Xu round trip).  wait_first: picks / xin may be the previous kernel's output.
+    const int *picks;
+    const __nv_bfloat16 *xin;
+    const __half *suh0, *suh1;
+    int rows, x_stride, wait_first;
 };
 
 __device__ __forceinline__ bool expert_skipped(int e, int E, int shared_exl3, int e_lo, int e_hi) {
@@ -100,17 +107,60 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
     const int nb = blockIdx.x, split = blockIdx.y, u = blockIdx.z;               // split == rank in the cluster
     const int KT = a.K >> 4, NTILES = a.N >> 4;
 
-    // one round trip for everything the prologue needs (none of the three loads depends on another)
-    const int cnt = __ldcg(a.count);
-    const int e = __ldcg(a.ids + u);
-    int code = -1;
-    if (tid < 16 && tid < a.maxm) code = __ldcg(a.members + (size_t)u * a.maxm + tid);
     if (tid == 0) {
         for (int g = 0; g < NG; ++g) mbar_init(bars + g, 1);
         mbar_fence_init();
     }
-    if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
-    if (tid < 16) rows_sh[tid] = code >= 0 ? (code >> 5) * a.slots + (code & 31) : -1;
+    int cnt, e;
+    if (a.picks) {
+        // ---- grouping in the CTA: distinct expert number u of the window and its members, from the routing table
+        __shared__ uint32_t used_sh[32];
+        if (a.wait_first) pdl_wait();
+        if (tid < 32) used_sh[tid] = 0u;
+        __syncthreads();
+        const int np = a.rows * a.slots;
+        for (int i = tid; i < np; i += GEMV_THREADS) {
+            const int pk = __ldcg(a.picks + i);
+            if ((unsigned)pk < 1024u) atomicOr(&used_sh[pk >> 5], 1u << (pk & 31));
+        }
+        __syncthreads();
+        __shared__ int e_sh, cnt_sh;
+        if (warp == 0) {                                       // number u among the set bits: one bitmap word per lane
+            const uint32_t bts = used_sh[lane];
+            const int c = __popc(bts);
+            int incl = c;
+#pragma unroll
+            for (int d = 1; d < 32; d <<= 1) {
+                const int up = __shfl_up_sync(0xffffffffu, incl, d);
+                if (lane >= d) incl += up;
+            }
+            const int excl = incl - c;
+            if (lane == 31) cnt_sh = incl;
+            if (u >= excl && u < incl) e_sh = lane * 32 + (int)__fns(bts, 0, u - excl + 1);
+            if (lane == 31 && u >= incl) e_sh = -1;
+        }
+        __syncthreads();
+        e = e_sh; cnt = cnt_sh;
+        if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
+        if (warp == 0) {                                       // rows <= 16: one lane per row, ascending row order
+            int slot = -1;
+            if (lane < a.rows)
+                for (int sl = a.slots - 1; sl >= 0; --sl)
+                    if (__ldcg(a.picks + lane * a.slots + sl) == e) slot = sl;
+            const uint32_t ball = __ballot_sync(0xffffffffu, slot >= 0);
+            const int pos = __popc(ball & ((1u << lane) - 1u));
+            if (slot >= 0 && pos < 16) rows_sh[pos] = lane * a.slots + slot;
+            if (lane < 16 && lane >= __popc(ball)) rows_sh[lane] = -1;
+        }
+    } else {
+        // one round trip for everything the prologue needs (none of the three loads depends on another)
+        cnt = __ldcg(a.count);
+        e = __ldcg(a.ids + u);
+        int code = -1;
+        if (tid < 16 && tid < a.maxm) code = __ldcg(a.members + (size_t)u * a.maxm + tid);
+        if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
+        if (tid < 16) rows_sh[tid] = code >= 0 ? (code >> 5) * a.slots + (code & 31) : -1;
+    }
     __syncthreads();
 
     // ---- the whole item's packed words, in flight at once
@@ -130,24 +180,51 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
     int nmem = 0;
 #pragma unroll
     for (int m = 0; m < SETS * 8; ++m) nmem += rows_sh[m] >= 0;   // members come first
-    pdl_wait();                                   // X belongs to the kernel before this one
+    pdl_wait();                                   // X belongs to the kernel before this one (no-op after wait_first)
 
     // ---- stage the members' activations of this K range as (x_k, 0) pairs, permuted to the mma order:
     //      dword position of local k = 64 g + 16 T + 8 h + 2 t + b  is  g*64 + (2t + h)*8 + 2T + b.
     //      Rows of absent members are left as they are: an mma column depends on its own B column only, and the
     //      columns of absent members are never stored.
-    {
-        const int k0 = kt0 * 16, half = KC >> 1;
+    auto stage_pos = [](int kl) {
+        const int g = kl >> 6, TT = (kl >> 4) & 3, h = (kl >> 3) & 1, t = (kl >> 1) & 3;
+        return g * 64 + (2 * t + h) * 8 + 2 * TT;
+    };
+    const int k0 = kt0 * 16;
+    if (a.xin) {
+        // rotate the layer input here (upstream rot_in_kernel, native/exl3.cu:224-241): one warp per (matrix, member,
+        // 128-block of this K range): fp16(H(x * suh) / sqrt 128), the same butterflies and rounding as the kernel form
+        const int blocks = KC >> 7;
+        for (int it = warp; it < MATS * nmem * blocks; it += GEMV_THREADS / 32) {
+            const int blk = it % blocks, mm = it / blocks;
+            const int m = mm % nmem, mat = mm / nmem;
+            const int row = rows_sh[m] / a.slots;
+            const int kl = blk * 128 + 4 * lane;
+            const uint2 xv = __ldcg(reinterpret_cast<const uint2 *>(a.xin + (size_t)row * a.x_stride + k0 + kl));
+            const uint2 sv = __ldg(reinterpret_cast<const uint2 *>((mat ? a.suh1 : a.suh0) + (size_t)e * a.K + k0 + kl));
+            const __nv_bfloat162 x01 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.x),
+                                 x23 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.y);
+            const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv.x), s23 = *reinterpret_cast<const __half2 *>(&sv.y);
+            float v[4] = {__bfloat162float(x01.x) * __low2float(s01), __bfloat162float(x01.y) * __high2float(s01),
+                          __bfloat162float(x23.x) * __low2float(s23), __bfloat162float(x23.y) * __high2float(s23)};
+            fwht128(v, lane);
+            uint32_t r[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) r[j] = (uint32_t)__half_as_ushort(__float2half_rn(v[j] * HAD_SCALE));
+            uint32_t *dst = asm_ + ((size_t)mat * SETS * 8 + m) * AST;
+            *reinterpret_cast<uint2 *>(dst + stage_pos(kl)) = make_uint2(r[0], r[1]);
+            *reinterpret_cast<uint2 *>(dst + stage_pos(kl + 2)) = make_uint2(r[2], r[3]);
+        }
+    } else {
+        const int half = KC >> 1;
         const int items = MATS * nmem * half;
         for (int i = tid; i < items; i += GEMV_THREADS) {
             const int kp = i % half, mm = i / half;
             const int m = mm % nmem, mat = mm / nmem;
             const int p = rows_sh[m];
             const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>((mat ? a.X1 : a.X0) + (size_t)p * a.K + k0) + kp);
-            const int kl = 2 * kp;
-            const int g = kl >> 6, TT = (kl >> 4) & 3, h = (kl >> 3) & 1, t = (kl >> 1) & 3;
-            const int pos = g * 64 + (2 * t + h) * 8 + 2 * TT;
-            *reinterpret_cast<uint2 *>(asm_ + ((size_t)mat * SETS * 8 + m) * AST + pos) = make_uint2(v & 0xffffu, v >> 16);
+            *reinterpret_cast<uint2 *>(asm_ + ((size_t)mat * SETS * 8 + m) * AST + stage_pos(2 * kp)) =
+                make_uint2(v & 0xffffu, v >> 16);
         }
     }
     __syncthreads();

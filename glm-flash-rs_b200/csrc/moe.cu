@@ -8,6 +8,11 @@
 
 namespace gf {
 int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
+}
+struct glmflash_experts;
+namespace gf {
+int experts_run_fused(glmflash_experts *e, cudaStream_t s, const glmflash_weights *w, const void *input, int x_stride,
+                      const int32_t *picks, int rows);
 
 // out[r][d] = sum_{s < slots-1, expert computed here} w[r][s] * Y[r*slots+s][d]  (+ Y[shared pair] if computed here)
 // fp32, ascending slot order, shared last: the order of the oracle's combine.
@@ -103,16 +108,15 @@ extern "C" int glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_we
                                 const int32_t *picks, const float *route_w, int rows) {
     GF_REQUIRE(m && w && input && picks && route_w, "null argument");
     GF_REQUIRE(rows > 0 && rows <= m->cfg.max_rows, "rows outside the scratch bound");
-    if ((m->phases & 1) && glmflash_grouping_run(m->grouping, stream, picks, rows)) return -1;
-    const int32_t *ids = glmflash_grouping_ids(m->grouping), *count = glmflash_grouping_count(m->grouping),
-                  *members = glmflash_grouping_members(m->grouping);
     const float *Y;
     if (m->experts) {
-        if (glmflash_experts_run_rows(m->experts, stream, w, input, x_stride, picks, ids, count, members, rows,
-                                      m->cfg.max_rows))
-            return -1;
+        // windows of <= 16 rows: grouping and input rotation happen inside the expert kernels
+        if (experts_run_fused(m->experts, (cudaStream_t)stream, w, input, x_stride, picks, rows)) return -1;
         Y = glmflash_experts_y(m->experts);
     } else {
+        if ((m->phases & 1) && glmflash_grouping_run(m->grouping, stream, picks, rows)) return -1;
+        const int32_t *ids = glmflash_grouping_ids(m->grouping), *count = glmflash_grouping_count(m->grouping),
+                      *members = glmflash_grouping_members(m->grouping);
         if (glmflash_fast_experts_run(m->fast, stream, w, input, x_stride, picks, ids, count, members, rows,
                                       m->cfg.max_rows, w->suh_g == w->suh_u))
             return -1;

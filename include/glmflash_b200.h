@@ -168,7 +168,8 @@ void glmflash_moe_free(glmflash_moe *m);
 int  glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_weights *w, const void *input, int x_stride,
                       const int32_t *picks, const float *route_w, int rows);
 float *glmflash_moe_output(const glmflash_moe *m);
-/* Profiling aid: 1 = grouping, 2 / 4 / 8 = the three ExpertGpu phases above, 16 = combine (default 31). */
+/* Profiling aid: 1 = grouping, 2 / 4 / 8 = the three ExpertGpu phases above, 16 = combine (default 31).  For
+ * windows of <= 16 rows grouping and input rotation are fused into the gate/up kernel (bits 1 and 2 select nothing). */
 int  glmflash_moe_set_phases(glmflash_moe *m, int mask);
 /* Host-buffer convenience used by the end-to-end measurement: copies input / picks / route_w from host
  * memory, runs, copies out[rows][H] back, and synchronises the stream. */
