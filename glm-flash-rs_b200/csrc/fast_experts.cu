@@ -45,6 +45,11 @@
 namespace gf {
 int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
 
+// FG_PROBE (timing experiments only, wrong results): 1 = decode warps store the raw words instead of decoding,
+// 2 = epilogue warps skip their arithmetic, 4 = no packed-word loads (decode a constant).
+#ifndef FG_PROBE
+#define FG_PROBE 0
+#endif
 constexpr int FG_THREADS = 640;
 constexpr int FG_BM = 128, FG_BN = 128, FG_BK = 64;
 constexpr int FG_TILE_BYTES = FG_BM * FG_BK * 2;           // 16 KB: one 128 x 64 fp16 operand tile
@@ -354,6 +359,7 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                         const uint32_t n = it / C::STAGES;
                         if (!wait_or_abort(empty + slot, (n & 1) ^ 1, abort_flag, a.status, GF_STATUS_TMA_TIMEOUT)) { ok = false; break; }
                         unsigned char *st = stages + (size_t)slot * C::STAGE_BYTES;
+                        if (FG_PROBE & 16) { mbar_arrive(full + slot); continue; }   // no A loads
                         mbar_expect_tx(full + slot, t.ntiles * FG_TILE_BYTES);
                         tma_load_2d(st, map, s * FG_BK, t.row0, full + slot);
                         if (t.ntiles == 2) tma_load_2d(st + FG_TILE_BYTES, map, s * FG_BK, t.row0 + FG_BM, full + slot);
@@ -362,9 +368,15 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                 if (!ok) break;
             }
         } else if (warp == 1 && lane == 0) {
+            // One thread issues every MMA.  Its own instruction stream is the critical path of the tensor pipe, so the
+            // shared-memory descriptors are built once (stage 0) and advanced by adding constants: the address field
+            // counts 16-byte units, a stage is STAGE_BYTES apart, a K step of 16 halves is 32 bytes.
+            const uint64_t desc_a0 = umma_desc_sw128(smem_u32(stages));
+            const uint64_t desc_b0 = umma_desc_sw128(smem_u32(stages) + 2 * FG_TILE_BYTES);
             uint32_t it = 0, pc = 0;
             for (int item = blockIdx.x; item < total && !*abort_flag; item += gridDim.x) {
                 const ItemInfo t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
+                const bool two = t.ntiles == 2;
                 bool ok = true;
                 for (int pm = 0; pm < MATS && ok; ++pm, ++pc) {
                     const uint32_t pb = pc & 1;
@@ -372,18 +384,23 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                     tc_fence_after();
                     const uint32_t d0 = tmem_base + pb * 256;
                     for (int s = 0; s < KS; ++s, ++it) {
-                        const int slot = it % C::STAGES;
+                        const uint32_t slot = it % C::STAGES;
                         const uint32_t n = it / C::STAGES;
                         if (!wait_or_abort(full + slot, n & 1, abort_flag, a.status, GF_STATUS_MMA_TIMEOUT)) { ok = false; break; }
                         tc_fence_after();
-                        const uint32_t sa = smem_u32(stages + (size_t)slot * C::STAGE_BYTES);
-                        const uint32_t sb = sa + 2 * FG_TILE_BYTES;
+                        const uint64_t da = desc_a0 + (uint64_t)(slot * (C::STAGE_BYTES >> 4));
+                        const uint64_t db = desc_b0 + (uint64_t)(slot * (C::STAGE_BYTES >> 4));
+                        const uint32_t acc0 = s > 0 ? 1u : 0u;
+                        if (two) {
 #pragma unroll
-                        for (int kk = 0; kk < FG_BK / 16; ++kk) {
-                            const uint32_t acc = (s > 0 || kk > 0) ? 1u : 0u;
-                            const uint64_t bd = umma_desc_sw128(sb + kk * 32);
-                            umma_f16(d0, umma_desc_sw128(sa + kk * 32), bd, UMMA_IDESC, acc);
-                            if (t.ntiles == 2) umma_f16(d0 + FG_BN, umma_desc_sw128(sa + FG_TILE_BYTES + kk * 32), bd, UMMA_IDESC, acc);
+                            for (int kk = 0; kk < FG_BK / 16; ++kk) {
+                                umma_f16(d0, da + 2 * kk, db + 2 * kk, UMMA_IDESC, kk > 0 ? 1u : acc0);
+                                umma_f16(d0 + FG_BN, da + (FG_TILE_BYTES >> 4) + 2 * kk, db + 2 * kk, UMMA_IDESC, kk > 0 ? 1u : acc0);
+                            }
+                        } else {
+#pragma unroll
+                            for (int kk = 0; kk < FG_BK / 16; ++kk)
+                                umma_f16(d0, da + 2 * kk, db + 2 * kk, UMMA_IDESC, kk > 0 ? 1u : acc0);
                         }
                         umma_commit(empty + slot);          // the stage may be overwritten once these MMAs have read it
                     }
@@ -426,6 +443,10 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                 __syncwarp();
                 if (lane == 0) mbar_arrive(tmem_empty + pb);             // this warp's rows are in registers
                 if (!has) continue;
+                if (FG_PROBE & 2) {
+                    if (v[5] == 1.2345f && m < cnt) a.status[1] = 1;
+                    continue;
+                }
                 fwht128_regs(v);
                 if (MATS == 2 && pm == 0) {
                     // gate: scale, bf16 rounding, clamp, silu (rounded) -> two bf16 per word, this thread's column of gbuf
@@ -492,7 +513,7 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         };
         auto load_words = [&](const uint32_t *src, uint32_t (&w)[NTL]) {
 #pragma unroll
-            for (int i = 0; i < NTL; ++i) w[i] = __ldg(src + i * 32);
+            for (int i = 0; i < NTL; ++i) w[i] = (FG_PROBE & 4) ? (uint32_t)(size_t)src : __ldg(src + i * 32);
         };
         auto do_stage = [&](const uint32_t (&wr)[NTL]) {
             const int slot = it % C::STAGES;
@@ -502,6 +523,15 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
 #pragma unroll
             for (int i = 0; i < NTL; ++i) {
                 const uint32_t w = wr[i];
+                if (FG_PROBE & 8) continue;                    // no stores at all
+                if (FG_PROBE & 1) {
+                    unsigned char *tbp = bt + i * 2048;
+                    *reinterpret_cast<uint32_t *>(tbp + off_lo0) = w;
+                    *reinterpret_cast<uint32_t *>(tbp + off_lo1) = w;
+                    *reinterpret_cast<uint32_t *>(tbp + off_lo0 + 1024) = w;
+                    *reinterpret_cast<uint32_t *>(tbp + off_lo1 + 1024) = w;
+                    continue;
+                }
                 const uint32_t pw = __shfl_sync(0xffffffffu, w, (lane + 31) & 31);
                 uint32_t x0, x1, x2, x3, x4, x5, x6, x7;
                 codeword_pair(__funnelshift_r(w, pw, 12), x0, x4);     // j = 0 | 4
