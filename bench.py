@@ -171,25 +171,17 @@ def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
     ps, ws = np.stack([r[0] for r in routes]), np.stack([r[1] for r in routes])
     x_d = torch.from_numpy(xs.view(np.int16)).to(dev).view(torch.bfloat16)
     p_d, w_d = torch.from_numpy(ps).to(dev), torch.from_numpy(ws).to(dev)
-    lo, hi = rank * (E // G), (rank + 1) * (E // G)
-    # the shared expert's 4096 rows go to one rank per layer (round robin)
-    moes = {sh: pkg.Moe(pkg.make_config(H, I, E, S, max_rows=R, shared_exl3=sh, expert_lo=lo, expert_hi=hi))
-            for sh in ((0, 1) if G > 1 else (1,))}
-    owner = lambda l: moes[1 if (G == 1 or l % G == rank) else 0]
-    if G > 1:
-        gathered = torch.empty((G, R, H), dtype=torch.float32, device=dev)
-        final = torch.empty((R, H), dtype=torch.float32, device=dev)
+    # the shared expert's rows go to one rank per layer (round robin)
+    from glmflash_b200 import ep
+    epm = ep.EpMoe(pkg, rank, G, R, H, I, E, S, device=dev, exchange=args.exchange)
+    owner = epm.owner
     stream = torch.cuda.Stream()
     state = {"i": 0}
 
     def step():
         l = state["i"] % L
         state["i"] += 1
-        m = owner(l)
-        m.run(structs[l], x_d[l], p_d[l], w_d[l], R)
-        if G > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
-            pkg.rank_sum(gathered, final)
+        epm.run(l, structs[l], x_d[l], p_d[l], w_d[l], R)
 
     def timed(fn, steps, warmup):
         with torch.cuda.stream(stream):
@@ -223,15 +215,21 @@ def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
     ph, wh = torch.from_numpy(ps).pin_memory(), torch.from_numpy(ws).pin_memory()
     oh = torch.empty((R, H), dtype=torch.float32).pin_memory()
 
+    x_stage = torch.empty((R, H), dtype=torch.bfloat16, device=dev)
+    p_stage = torch.empty((R, S), dtype=torch.int32, device=dev)
+    w_stage = torch.empty((R, S), dtype=torch.float32, device=dev)
+
     def step_e2e():
         l = state["i"] % L
         state["i"] += 1
-        m = owner(l)
-        m.run_host(structs[l], xh[l], ph[l], wh[l], R, oh, stream=stream)
-        if G > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
-            pkg.rank_sum(gathered, final, stream=stream)
-            oh.copy_(final, non_blocking=True)
+        if G == 1:
+            owner(l).run_host(structs[l], xh[l], ph[l], wh[l], R, oh, stream=stream)
+        else:
+            x_stage.view(torch.int16).copy_(xh[l], non_blocking=True)
+            p_stage.copy_(ph[l], non_blocking=True)
+            w_stage.copy_(wh[l], non_blocking=True)
+            res = epm.run(l, structs[l], x_stage, p_stage, w_stage, R)
+            oh.copy_(res, non_blocking=True)
             stream.synchronize()
     ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3)
     e2e = {"value": R / (ms_e2e / 1e3), "unit": "layer-tokens/s", "ms_per_step": ms_e2e,
@@ -299,6 +297,7 @@ def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
                           "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True,
                           "scaling": "strong", "vs_baseline": None, "dtype": "f16xf16->f32", "data": "synthetic",
                           "config": workload_config(args), "tflops": flops / (ms_step * 1e-3) / 1e12, "clocks": clocks, "e2e": e2e,
+                          "exchange": epm.exchange,
                           "gpu_launches": 6 * args.steps, "roofline": roofline, "upstream_kernels_sm100a": upstream, "cpu_baseline": cpu}))
     finish(world, dist)
 
@@ -325,6 +324,8 @@ def main():
     ap.add_argument("--layers", type=int, default=47)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
+    ap.add_argument("--exchange", default="nvlink", choices=["nvlink", "nccl"],
+                    help="N > 1: fused combine + NVLink push + ordered sum kernel, or NCCL all-gather + ordered sum")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -366,21 +367,18 @@ def main():
     w_d = torch.from_numpy(ws).to(dev)
 
     # ---- owners: expert window per rank; the shared expert goes round robin over the layers
-    lo, hi = rank * (E // G), (rank + 1) * (E // G)
-    moes = {}
-    for sh in ((0, 1) if G > 1 else (1,)):
-        moes[sh] = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=max(R, 1), shared_exl3=sh, expert_lo=lo, expert_hi=hi))
-    owner = lambda l: moes[1 if (G == 1 or l % G == rank) else 0]
+    from glmflash_b200 import ep
+    epm = ep.EpMoe(pkg, rank, G, max(R, 1), H, I, E, S, device=dev, exchange=args.exchange)
+    owner = epm.owner
+    moes = epm.moes
     if G > 1:
-        gathered = torch.empty((G, R, H), dtype=torch.float32, device=dev)
         final = torch.empty((L, R, H), dtype=torch.float32, device=dev)
 
     def layer(l):
-        m = owner(l)
-        m.run(structs[l], x_d[l], p_d[l], w_d[l], R)
-        if G > 1:
-            dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
-            pkg.rank_sum(gathered, final[l])
+        if G == 1:
+            epm.run(l, structs[l], x_d[l], p_d[l], w_d[l], R)
+        else:
+            epm.run(l, structs[l], x_d[l], p_d[l], w_d[l], R, out=final[l])
 
     def step_eager():
         for l in range(L):
@@ -435,18 +433,21 @@ def main():
     xh = torch.from_numpy(xs.view(np.int16)).pin_memory()
     ph, wh = torch.from_numpy(ps).pin_memory(), torch.from_numpy(ws).pin_memory()
     oh = torch.empty((L, R, H), dtype=torch.float32).pin_memory()
-    part_h = torch.empty((R, H), dtype=torch.float32).pin_memory()
+
+    x_stage = torch.empty((R, H), dtype=torch.bfloat16, device=dev)
+    p_stage = torch.empty((R, S), dtype=torch.int32, device=dev)
+    w_stage = torch.empty((R, S), dtype=torch.float32, device=dev)
 
     def step_e2e():
         for l in range(L):
-            m = owner(l)
             if G == 1:
-                m.run_host(structs[l], xh[l], ph[l], wh[l], R, oh[l], stream=stream)
-            else:                                                # partial on this rank, exchange, rank-ordered sum, read back
-                m.run_host(structs[l], xh[l], ph[l], wh[l], R, part_h, stream=stream)
-                dist.all_gather_into_tensor(gathered.view(-1), m.output[:R].reshape(-1))
-                pkg.rank_sum(gathered, final[l], stream=stream)
-                oh[l].copy_(final[l], non_blocking=True)
+                owner(l).run_host(structs[l], xh[l], ph[l], wh[l], R, oh[l], stream=stream)
+            else:                                                # host inputs in, this rank's experts, exchange, result out
+                x_stage.view(torch.int16).copy_(xh[l], non_blocking=True)
+                p_stage.copy_(ph[l], non_blocking=True)
+                w_stage.copy_(wh[l], non_blocking=True)
+                res = epm.run(l, structs[l], x_stage, p_stage, w_stage, R)
+                oh[l].copy_(res, non_blocking=True)
                 stream.synchronize()
     ms_e2e = timed(step_e2e, max(3, args.steps // 4), 3)
     e2e = {"value": R * L / (ms_e2e / 1e3), "unit": "layer-tokens/s", "ms_per_step": ms_e2e,
@@ -494,7 +495,8 @@ def main():
                "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                "dtype": "f16xf16->f32", "data": "synthetic", "config": workload_config(args),
                "stack_tokens_per_s": R / (ms_step / 1e3), "graph": graph is not None,
-               "clocks": clocks, "e2e": e2e, "gpu_launches": 5 * L * args.steps + (0 if G == 1 else L * args.steps),
+               "clocks": clocks, "e2e": e2e, "exchange": epm.exchange,
+               "gpu_launches": (3 if G == 1 or epm.exchange == "nvlink" else 4) * L * args.steps,
                "roofline": roofline, "cpu_baseline": cpu}
         print(json.dumps(out))
     finish(world, dist)

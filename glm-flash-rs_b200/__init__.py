@@ -63,9 +63,18 @@ SYMBOLS = {
     "glmflash_moe_free": (None, [_P]),
     "glmflash_moe_run": (_I, [_P, _P, _P, _P, _I, _P, _P, _I]),
     "glmflash_moe_output": (_P, [_P]),
+    "glmflash_moe_pairs": (_P, [_P]),
     "glmflash_moe_set_phases": (_I, [_P, _I]),
     "glmflash_moe_run_host": (_I, [_P, _P, _P, _P, _I, _P, _P, _I, _P]),
     "glmflash_rank_sum": (_I, [_P, _P, _I, _I, _I, _P]),
+    "glmflash_ep_handle_bytes": (_Z, []),
+    "glmflash_ep_new": (_I, [_P, _Z, _I, _I, _P]),
+    "glmflash_ep_free": (None, [_P]),
+    "glmflash_ep_get_handle": (_I, [_P, _P]),
+    "glmflash_ep_connect": (_I, [_P, _P]),
+    "glmflash_ep_combine": (_I, [_P, _P, _P, _P, _P, _I, _I]),
+    "glmflash_ep_output": (_P, [_P]),
+    "glmflash_ep_status": (_P, [_P]),
 }
 
 _lib = None
@@ -305,6 +314,11 @@ class Moe(_Owner):
         _check(lib().glmflash_moe_set_phases(self._h, mask))
 
     @property
+    def pairs_ptr(self):
+        """Device address of the pair results Y fp32 [rows*slots][H] of the last run."""
+        return C.c_void_p(lib().glmflash_moe_pairs(self._h))
+
+    @property
     def output(self):
         import torch
         return _view(lib().glmflash_moe_output(self._h), (self.cfg.max_rows, self.cfg.hidden), torch.float32)
@@ -315,3 +329,48 @@ def rank_sum(gathered, out, stream=None):
     world, rows, H = gathered.shape
     _check(lib().glmflash_rank_sum(_stream_ptr(stream), gathered.data_ptr(), world, rows, H, out.data_ptr()))
     return out
+
+
+class EpCombine:
+    """glmflash_ep_*: combine fused with the cross-GPU exchange over NVLink (one owner per rank).
+    `exchange_handles(local_bytes) -> list of every rank's bytes in rank order` is the host's bootstrap channel
+    (torch.distributed.all_gather_object in the tests and the benchmark)."""
+
+    def __init__(self, cfg, rank, world, exchange_handles):
+        _torch()
+        self.cfg, self.rank, self.world = cfg, rank, world
+        self._h = C.c_void_p()
+        _check(lib().glmflash_ep_new(C.byref(cfg), C.sizeof(cfg), rank, world, C.byref(self._h)))
+        if world > 1:
+            n = lib().glmflash_ep_handle_bytes()
+            buf = C.create_string_buffer(n)
+            _check(lib().glmflash_ep_get_handle(self._h, buf))
+            allh = exchange_handles(bytes(buf.raw))
+            assert len(allh) == world and all(len(b) == n for b in allh)
+            _check(lib().glmflash_ep_connect(self._h, C.create_string_buffer(b"".join(allh), n * world)))
+
+    def combine(self, Y_ptr, picks, route_w, rows, shared_here, stream=None):
+        _check(lib().glmflash_ep_combine(self._h, _stream_ptr(stream), Y_ptr, picks.data_ptr(), route_w.data_ptr(), rows,
+                                         int(shared_here)))
+        return self.output[:rows]
+
+    @property
+    def output(self):
+        import torch
+        return _view(lib().glmflash_ep_output(self._h), (self.cfg.max_rows, self.cfg.hidden), torch.float32)
+
+    @property
+    def status(self):
+        import torch
+        return _view(lib().glmflash_ep_status(self._h), (1,), torch.int32)
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            lib().glmflash_ep_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -6,6 +6,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <string.h>
+
 #include <string>
 
 #include "../../include/glmflash_b200.h"
@@ -198,6 +200,6 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t (&a)[4], 
 }
 
 // Device status word shared by kernels with bounded waits: 0 = fine, otherwise the first failure code.
-enum : int { GF_STATUS_OK = 0, GF_STATUS_TMA_TIMEOUT = 1, GF_STATUS_TMEM = 2, GF_STATUS_MMA_TIMEOUT = 3 };
+enum : int { GF_STATUS_OK = 0, GF_STATUS_TMA_TIMEOUT = 1, GF_STATUS_TMEM = 2, GF_STATUS_MMA_TIMEOUT = 3, GF_STATUS_PEER_TIMEOUT = 4 };
 
 }  // namespace gf

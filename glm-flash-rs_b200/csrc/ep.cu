@@ -1,0 +1,208 @@
+// Expert-parallel combine fused with its exchange over NVLink (one process per GPU).
+//
+// Upstream gathers every rank's fp32 partial layer output with an all-gather (NCCL, or its one-shot RoCE gather
+// kernel, native/roce.cu:217-371) and then adds the ranks' rows in fixed rank order (src/model.rs:485-496,
+// src/comm.rs:1-2).  Here one kernel per rank does the whole step:
+//   1. combine: partial[r][:] = sum of this rank's pairs of row r (weights applied), as combine_kernel;
+//   2. push:    the partial is stored straight into slot `rank` of EVERY peer's receive buffer through peer-mapped
+//               pointers (plain st.global over NVLink, no multicast), then a release fence and one flag word per
+//               (source rank, CTA) carries the epoch;
+//   3. wait:    the same CTA spins (bounded) on its own GPU's flags until every source has delivered the epoch;
+//   4. sum:     the slots are added in ascending rank order -- the reference's determinism rule -- into out.
+// Receive buffers are double-buffered by epoch parity; the epoch lives in device memory and is advanced by the
+// last CTA of a call, so captured graphs replay correctly.  A wait that gives up sets the status word (the
+// analogue of upstream's poison word, native/roce.cu:127-141) and the kernel returns; nothing spins unbounded.
+#include <new>
+#include <vector>
+
+#include "common.cuh"
+
+namespace gf {
+int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
+
+constexpr int EP_MAX_WORLD = 8;
+constexpr int EP_THREADS = 256;
+
+struct EpPeers {
+    float *recv[EP_MAX_WORLD];          // recv[k]: rank k's receive buffer [2][world][max_rows][H] (peer-mapped)
+    unsigned *flags[EP_MAX_WORLD];      // flags[k]: rank k's flags [2][world][max_ctas]
+};
+
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
+                                                                const float *__restrict__ route_w, float *__restrict__ out,
+                                                                EpPeers peers, unsigned *epoch_ptr, unsigned *done_ptr,
+                                                                int *status, int rank, int world, int rows, int max_rows,
+                                                                int max_ctas, int slots, int H, int E, int shared_exl3,
+                                                                int e_lo, int e_hi) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ int ok_sh;
+    const int r = blockIdx.y;
+    const int cta = blockIdx.y * gridDim.x + blockIdx.x;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const unsigned epoch = *epoch_ptr + 1u;                   // every CTA reads it before the last one advances it
+    const unsigned par = epoch & 1u;
+    const size_t slot_elems = (size_t)max_rows * H;
+    // 1. this rank's partial of row r
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (d < H) {
+        for (int s = 0; s < slots; ++s) {
+            const int e = picks[r * slots + s];
+            const bool skip = e < 0 || (e >= E ? !shared_exl3 : (e < e_lo || e >= e_hi));
+            if (skip) continue;
+            const float4 y = *reinterpret_cast<const float4 *>(Y + ((size_t)r * slots + s) * H + d);
+            if (s == slots - 1) { acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w; }
+            else {
+                const float w = route_w[r * slots + s];
+                acc.x += w * y.x; acc.y += w * y.y; acc.z += w * y.z; acc.w += w * y.w;
+            }
+        }
+        // 2. push into slot `rank` of every rank's receive buffer (its own included)
+        for (int k = 0; k < world; ++k) {
+            float *dst = peers.recv[k] + ((size_t)par * world + rank) * slot_elems + (size_t)r * H + d;
+            *reinterpret_cast<float4 *>(dst) = acc;
+        }
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < world)
+        st_release_sys(peers.flags[threadIdx.x] + ((size_t)par * world + rank) * max_ctas + cta, epoch);
+    // 3. wait for every source's copy of this CTA's region
+    if (threadIdx.x == 0) ok_sh = 1;
+    __syncthreads();
+    if (threadIdx.x < world) {
+        const unsigned *f = peers.flags[rank] + ((size_t)par * world + threadIdx.x) * max_ctas + cta;
+        bool got = false;
+        for (unsigned i = 0; i < 20000000u; ++i) {
+            if (ld_acquire_sys(f) == epoch) { got = true; break; }
+            if ((i & 1023u) == 1023u) __nanosleep(200);
+        }
+        if (!got) { ok_sh = 0; atomicExch(status, GF_STATUS_PEER_TIMEOUT); }
+    }
+    __syncthreads();
+    // 4. ordered sum
+    if (d < H && ok_sh) {
+        const float *src = peers.recv[rank] + (size_t)par * world * slot_elems + (size_t)r * H + d;
+        float4 sum = __ldcg(reinterpret_cast<const float4 *>(src));
+        for (int k = 1; k < world; ++k) {
+            const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)k * slot_elems));
+            sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+        }
+        *reinterpret_cast<float4 *>(out + (size_t)r * H + d) = sum;
+    }
+    // the last CTA of the call advances the epoch (after every CTA has read it)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned n = gridDim.x * gridDim.y;
+        if (atomicAdd(done_ptr, 1u) == n - 1u) {
+            *done_ptr = 0u;
+            __threadfence();
+            *epoch_ptr = epoch;
+        }
+    }
+}
+}  // namespace gf
+
+using namespace gf;
+
+struct glmflash_ep {
+    glmflash_config cfg;
+    int rank = 0, world = 1, max_ctas = 0;
+    unsigned char *local = nullptr;               // one allocation: recv | flags | epoch | done | status
+    size_t recv_bytes = 0, flag_bytes = 0, total_bytes = 0;
+    void *peer_base[EP_MAX_WORLD] = {};
+    bool opened[EP_MAX_WORLD] = {};
+    bool connected = false;
+    float *out = nullptr;
+};
+
+extern "C" size_t glmflash_ep_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+
+extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int rank, int world, glmflash_ep **out) {
+    GF_REQUIRE(out != nullptr, "out is null");
+    *out = nullptr;
+    if (check_config(cfg, cfg_bytes, 8192)) return -1;
+    GF_REQUIRE(world >= 1 && world <= EP_MAX_WORLD && rank >= 0 && rank < world, "rank / world out of range (world <= 8)");
+    glmflash_ep *h = new (std::nothrow) glmflash_ep();
+    GF_REQUIRE(h != nullptr, "out of host memory");
+    h->cfg = *cfg; h->rank = rank; h->world = world;
+    const size_t H = cfg->hidden, R = cfg->max_rows;
+    h->max_ctas = (int)(((H / 4 + EP_THREADS - 1) / EP_THREADS) * R);
+    h->recv_bytes = (size_t)2 * world * R * H * 4;
+    h->flag_bytes = ((size_t)2 * world * h->max_ctas * 4 + 255) / 256 * 256;
+    h->total_bytes = h->recv_bytes + h->flag_bytes + 256;
+    if (cudaMalloc((void **)&h->local, h->total_bytes) != cudaSuccess || cudaMemset(h->local, 0, h->total_bytes) != cudaSuccess ||
+        cudaMalloc((void **)&h->out, R * H * 4) != cudaSuccess) {
+        glmflash_ep_free(h);
+        return fail("cudaMalloc(ep buffers) failed");
+    }
+    h->peer_base[rank] = h->local;
+    if (world == 1) h->connected = true;
+    *out = h;
+    return 0;
+}
+
+extern "C" void glmflash_ep_free(glmflash_ep *h) {
+    if (!h) return;
+    for (int k = 0; k < h->world; ++k)
+        if (h->opened[k]) cudaIpcCloseMemHandle(h->peer_base[k]);
+    cudaFree(h->local); cudaFree(h->out);
+    delete h;
+}
+
+extern "C" int glmflash_ep_get_handle(glmflash_ep *h, void *handle_out) {
+    GF_REQUIRE(h && handle_out, "null argument");
+    cudaIpcMemHandle_t m;
+    GF_CUDA(cudaIpcGetMemHandle(&m, h->local));
+    memcpy(handle_out, &m, sizeof(m));
+    return 0;
+}
+
+extern "C" int glmflash_ep_connect(glmflash_ep *h, const void *all_handles) {
+    GF_REQUIRE(h && all_handles, "null argument");
+    GF_REQUIRE(!h->connected, "already connected");
+    const unsigned char *p = (const unsigned char *)all_handles;
+    for (int k = 0; k < h->world; ++k) {
+        if (k == h->rank) continue;
+        cudaIpcMemHandle_t m;
+        memcpy(&m, p + (size_t)k * sizeof(m), sizeof(m));
+        void *base = nullptr;
+        GF_CUDA(cudaIpcOpenMemHandle(&base, m, cudaIpcMemLazyEnablePeerAccess));
+        h->peer_base[k] = base;
+        h->opened[k] = true;
+    }
+    h->connected = true;
+    return 0;
+}
+
+extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y, const int32_t *picks, const float *route_w,
+                                   int rows, int shared_here) {
+    GF_REQUIRE(h && Y && picks && route_w, "null argument");
+    GF_REQUIRE(h->connected, "glmflash_ep_connect has not been called");
+    GF_REQUIRE(rows > 0 && rows <= h->cfg.max_rows, "rows outside the scratch bound");
+    const glmflash_config &c = h->cfg;
+    EpPeers peers{};
+    for (int k = 0; k < h->world; ++k) {
+        peers.recv[k] = (float *)h->peer_base[k];
+        peers.flags[k] = (unsigned *)((unsigned char *)h->peer_base[k] + h->recv_bytes);
+    }
+    unsigned *epoch = (unsigned *)(h->local + h->recv_bytes + h->flag_bytes);
+    const dim3 grid((unsigned)((c.hidden / 4 + EP_THREADS - 1) / EP_THREADS), (unsigned)rows);
+    return launch_k(ep_combine_kernel, grid, dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w, h->out,
+                    peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas, c.slots,
+                    c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi);
+}
+
+extern "C" float *glmflash_ep_output(const glmflash_ep *h) { return h ? h->out : nullptr; }
+extern "C" const int32_t *glmflash_ep_status(const glmflash_ep *h) {
+    return h ? (const int32_t *)(h->local + h->recv_bytes + h->flag_bytes + 8) : nullptr;
+}

@@ -128,12 +128,16 @@ extern "C" int glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_we
 
 extern "C" int glmflash_moe_set_phases(glmflash_moe *m, int mask) {
     GF_REQUIRE(m != nullptr, "null argument");
-    GF_REQUIRE(m->experts != nullptr, "phase selection exists for the decode / verify pipeline only");
     m->phases = mask;
-    return glmflash_experts_set_phases(m->experts, (mask >> 1) & 7);
+    if (m->experts) return glmflash_experts_set_phases(m->experts, (mask >> 1) & 7);
+    return 0;                                      // prefill pipeline: only grouping (1) and combine (16) are selectable here
 }
 
 extern "C" float *glmflash_moe_output(const glmflash_moe *m) { return m ? m->out : nullptr; }
+extern "C" const float *glmflash_moe_pairs(const glmflash_moe *m) {
+    if (!m) return nullptr;
+    return m->experts ? glmflash_experts_y(m->experts) : glmflash_fast_experts_output(m->fast);
+}
 
 extern "C" int glmflash_moe_run_host(glmflash_moe *m, void *stream, const glmflash_weights *w, const void *input_host,
                                      int x_stride, const int32_t *picks_host, const float *route_w_host, int rows,

@@ -55,28 +55,51 @@ def exchange(partial, gathered, out, group=None, rank_sum=None):
 
 class EpMoe:
     """One MoE layer call, expert parallel: Moe handles with this rank's window (with and without the shared
-    expert), the exchange buffers, and run(layer, ...) -> final [rows][H] on every rank."""
+    expert) and run(layer, ...) -> final [rows][H] on every rank.
+    exchange = "nvlink": the library's fused combine + NVLink push + ordered sum kernel (glmflash_ep_combine);
+    exchange = "nccl":   local combine, NCCL all-gather of the partials, rank-ordered sum kernel (the baseline)."""
 
-    def __init__(self, pkg, rank, world, max_rows, hidden=2048, inter=1536, experts=64, slots=5, group=None, device=None):
+    def __init__(self, pkg, rank, world, max_rows, hidden=2048, inter=1536, experts=64, slots=5, group=None, device=None,
+                 exchange="nvlink"):
         import torch
+        import torch.distributed as dist
         self.pkg, self.rank, self.world, self.group = pkg, rank, world, group
-        self.experts, self.hidden = experts, hidden
+        self.experts, self.hidden, self.exchange = experts, hidden, exchange if world > 1 else "none"
         lo, hi = expert_window(rank, world, experts)
         kinds = (1,) if world == 1 else (0, 1)
         self.moes = {sh: pkg.Moe(pkg.make_config(hidden, inter, experts, slots, max_rows=max_rows, shared_exl3=sh,
                                                  expert_lo=lo, expert_hi=hi)) for sh in kinds}
-        if world > 1:
+        if self.exchange == "nccl":
             self.gathered = torch.empty((world, max_rows, hidden), dtype=torch.float32, device=device)
             self.final = torch.empty((max_rows, hidden), dtype=torch.float32, device=device)
+        elif self.exchange == "nvlink":
+            def gather(local):
+                out = [None] * world
+                dist.all_gather_object(out, local, group=group)
+                return out
+            cfg = pkg.make_config(hidden, inter, experts, slots, max_rows=max_rows, shared_exl3=0, expert_lo=lo, expert_hi=hi)
+            self.ep = pkg.EpCombine(cfg, rank, world, gather)
+            for m in self.moes.values():
+                m.set_phases(15)                    # experts only: the combine is the fused exchange kernel's first step
+
+    def owns_shared(self, layer):
+        return self.world == 1 or shared_owner(layer, self.world) == self.rank
 
     def owner(self, layer):
-        return self.moes[1 if (self.world == 1 or shared_owner(layer, self.world) == self.rank) else 0]
+        return self.moes[1 if self.owns_shared(layer) else 0]
 
     def run(self, layer, w, x, picks, route_w, rows, out=None, stream=None):
         m = self.owner(layer)
         m.run(w, x, picks, route_w, rows, stream=stream)
-        if self.world == 1:
+        if self.exchange == "none":
             return m.output[:rows]
+        if self.exchange == "nvlink":
+            res = self.ep.combine(m.pairs_ptr, picks, route_w, rows, self.owns_shared(layer), stream=stream)
+            if out is not None:
+                out.copy_(res)
+                return out
+            return res
         out = self.final[:rows] if out is None else out
-        g = self.gathered[:, :rows] if rows == self.gathered.shape[1] else self.gathered.view(-1)[: self.world * rows * self.hidden].view(self.world, rows, self.hidden)
+        g = self.gathered if rows == self.gathered.shape[1] else \
+            self.gathered.view(-1)[: self.world * rows * self.hidden].view(self.world, rows, self.hidden)
         return exchange(m.output[:rows], g, out, self.group, lambda a, b: self.pkg.rank_sum(a, b, stream=stream))

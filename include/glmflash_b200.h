@@ -168,6 +168,8 @@ void glmflash_moe_free(glmflash_moe *m);
 int  glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_weights *w, const void *input, int x_stride,
                       const int32_t *picks, const float *route_w, int rows);
 float *glmflash_moe_output(const glmflash_moe *m);
+/* The pair results Y fp32 [rows*slots][H] behind the last run (the ExpertGpu / FastExperts output of this owner). */
+const float *glmflash_moe_pairs(const glmflash_moe *m);
 /* Profiling aid: 1 = grouping, 2 / 4 / 8 = the three ExpertGpu phases above, 16 = combine (default 31).  For
  * windows of <= 16 rows grouping and input rotation are fused into the gate/up kernel (bits 1 and 2 select nothing). */
 int  glmflash_moe_set_phases(glmflash_moe *m, int mask);
@@ -178,6 +180,28 @@ int  glmflash_moe_run_host(glmflash_moe *m, void *stream, const glmflash_weights
                            float *out_host);
 
 /* ---- expert-parallel combine over NVLink ------------------------------------------------------------ */
+/* One owner per rank (one process per GPU).  It replaces upstream's gather + ordered sum after the MoE layer
+ * (src/model.rs:485-496; Nccl::all_gather_f32 src/comm.rs:261-285 / Roce::gather src/roce.rs:283-330) by ONE kernel
+ * per rank: combine this rank's pairs, store the partial into every peer's receive slot over NVLink (peer-mapped
+ * memory, plain stores), signal, wait (bounded) for the peers' partials and add the slots in rank order.
+ * Set-up mirrors upstream's bootstrap (src/comm.rs:109-162): every rank creates its owner, publishes an opaque
+ * handle of glmflash_ep_handle_bytes() bytes, receives all ranks' handles (in rank order, by whatever channel the
+ * host has: TCP, torch.distributed, ...) and calls glmflash_ep_connect once.  Every rank must then call
+ * glmflash_ep_combine the same number of times in the same order.  A peer that never arrives makes the wait give up
+ * after a bounded number of polls: the status word becomes non-zero and the output of that call is undefined. */
+typedef struct glmflash_ep glmflash_ep;
+size_t glmflash_ep_handle_bytes(void);
+int  glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int rank, int world, glmflash_ep **out);
+void glmflash_ep_free(glmflash_ep *h);
+int  glmflash_ep_get_handle(glmflash_ep *h, void *handle_out);
+int  glmflash_ep_connect(glmflash_ep *h, const void *all_handles /* world x handle_bytes, rank order */);
+/* Y: fp32 [rows*slots][H] pair results of this rank (glmflash_moe_pairs); the config's expert window decides which
+ * routed pairs are this rank's, shared_here whether the shared expert's pair is (it may move from layer to layer).
+ * Result: glmflash_ep_output() fp32 [rows][H]. */
+int  glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y, const int32_t *picks, const float *route_w, int rows,
+                         int shared_here);
+float *glmflash_ep_output(const glmflash_ep *h);
+const int32_t *glmflash_ep_status(const glmflash_ep *h);
 /* out[r][:] = sum over ranks (ascending rank order) of gathered[rank][r][:], the fixed-order sum upstream
  * applies after its all-gather (src/model.rs:485-496, src/comm.rs:1-2).  gathered: fp32 [world][rows][H]. */
 int glmflash_rank_sum(void *stream, const float *gathered, int world, int rows, int hidden, float *out);

@@ -35,7 +35,8 @@ def _worker(rank, world, port, rows_list, q):
     try:
         res = []
         for rows in rows_list:
-            layer = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev)
+            layer = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nvlink")
+            base = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nccl")
             single = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows))
             for l in range(2):
                 bank = synth.device_bank(300 + l, H, I, E, dev)
@@ -43,8 +44,13 @@ def _worker(rank, world, port, rows_list, q):
                 picks, rw = synth.route(320 + l, rows, E, S - 1, shared_bias=rows <= 16, uniform=rows > 16)
                 pd, wd = torch.from_numpy(picks).to(dev), torch.from_numpy(rw).to(dev)
                 out = layer.run(l, bank, x, pd, wd, rows).clone()
+                for _ in range(3):                                  # epochs advance in lockstep, buffers alternate
+                    again = layer.run(l, bank, x, pd, wd, rows).clone()
+                nccl = base.run(l, bank, x, pd, wd, rows).clone()
                 single.run(bank, x, pd, wd, rows)
                 torch.cuda.synchronize()
+                assert int(layer.ep.status.cpu()[0]) == 0, "a bounded peer wait gave up"
+                assert torch.equal(out, again) and torch.equal(out, nccl), "fused NVLink exchange != NCCL all-gather + ordered sum"
                 ref = single.output[:rows].clone()
                 chk = [torch.empty_like(out) for _ in range(world)]
                 dist.all_gather(chk, out)
