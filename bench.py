@@ -262,7 +262,9 @@ def run_prefill(args, pkg, synth, torch, dist, dev, rank, world, local):
         ach = gu_flops / (ms_gu * 1e-3) / 1e12
         roofline = {"bound": "tensor", "kernel": "fast_gemm_kernel<2> (gate/up grouped GEMM: tcgen05 + in-kernel trellis decode + SwiGLU epilogue)",
                     "achieved": ach, "peak": peak, "peak_source": how, "unit": "TFLOP/s", "frac": ach / peak, "ms_per_launch": ms_gu,
-                    "algorithmic_flops_per_launch": gu_flops, "traffic": None,
+                    "algorithmic_flops_per_launch": gu_flops,
+                    # dram bytes of one launch from the capture in profiles/fast_gemm_prefill_4096.md (500.6 MB + 65.4 MB)
+                    "traffic": 566022912.0 if R == 4096 else None,
                     "down_kernel": {"ms_per_launch": ms_dn, "tflops": R * S * 2 * H * I / (ms_dn * 1e-3) / 1e12},
                     "layer": {"tflops": flops / (ms_step * 1e-3) / 1e12, "frac": flops / (ms_step * 1e-3) / 1e12 / peak}}
         # the reference's own CUDA kernels, recompiled unmodified for sm_100a, on the same tensors (comparison only)
@@ -478,7 +480,10 @@ def main():
         roofline = {"bound": "hbm", "kernel": "gemv_kernel<2,*> (gate/up grouped GEMV + SwiGLU epilogue)", "achieved": achieved,
                     "peak": peak, "peak_source": how + " (MEASURED_PEAKS.json hbm_gbs)" if how == "measured" else how,
                     "unit": "GB/s", "frac": achieved / peak, "us_per_launch": ms_pass / L * 1e3,
-                    "algorithmic_bytes_per_launch": bytes_per_launch, "traffic": None,
+                    "algorithmic_bytes_per_launch": bytes_per_launch,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the ncu capture summarised in
+                    # profiles/gemv_decode_bs1.md (1 token: 15.88 MB read, 0 written); other row counts were not captured
+                    "traffic": 15880192.0 if R == 1 else None,
                     "layer": {"algorithmic_bytes": float(np.mean(distinct)) * W_E + R * H * 6, "us": ms_step / L * 1e3,
                               "gbs": (float(np.mean(distinct)) * W_E + R * H * 6) / (ms_step / L * 1e-3) / 1e9}}
         roofline["layer"]["frac"] = roofline["layer"]["gbs"] / peak
