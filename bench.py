@@ -431,30 +431,54 @@ def main():
     ms_step = timed(step, args.steps, args.warmup)
     value = R * L / (ms_step / 1e3)
 
-    # ---- end to end: pinned host buffers through the host-buffer C-ABI call, every layer, every step
+    # ---- end to end: every step copies the step's inputs (all layers' activations, routing tables, routing weights)
+    #      from pinned host memory, runs the 47 layer calls of the public API on them, and reads all layer outputs back
     xh = torch.from_numpy(xs.view(np.int16)).pin_memory()
     ph, wh = torch.from_numpy(ps).pin_memory(), torch.from_numpy(ws).pin_memory()
     oh = torch.empty((L, R, H), dtype=torch.float32).pin_memory()
+    out_all = torch.empty((L, R, H), dtype=torch.float32, device=dev)
 
-    x_stage = torch.empty((R, H), dtype=torch.bfloat16, device=dev)
-    p_stage = torch.empty((R, S), dtype=torch.int32, device=dev)
-    w_stage = torch.empty((R, S), dtype=torch.float32, device=dev)
-
-    def step_e2e():
+    def layers_with_outputs():
         for l in range(L):
             if G == 1:
-                owner(l).run_host(structs[l], xh[l], ph[l], wh[l], R, oh[l], stream=stream)
-            else:                                                # host inputs in, this rank's experts, exchange, result out
-                x_stage.view(torch.int16).copy_(xh[l], non_blocking=True)
-                p_stage.copy_(ph[l], non_blocking=True)
-                w_stage.copy_(wh[l], non_blocking=True)
-                res = epm.run(l, structs[l], x_stage, p_stage, w_stage, R)
-                oh[l].copy_(res, non_blocking=True)
-                stream.synchronize()
-    ms_e2e = timed(step_e2e, max(3, args.steps // 4), 3)
+                out_all[l].copy_(epm.run(l, structs[l], x_d[l], p_d[l], w_d[l], R))
+            else:
+                epm.run(l, structs[l], x_d[l], p_d[l], w_d[l], R, out=out_all[l])
+    graph_e2e = None
+    with torch.cuda.stream(stream):
+        layers_with_outputs()
+        stream.synchronize()
+        try:
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=stream):
+                layers_with_outputs()
+            graph_e2e = g2
+        except Exception:
+            torch.cuda.synchronize()
+
+    def step_e2e():
+        x_d.view(torch.int16).copy_(xh, non_blocking=True)
+        p_d.copy_(ph, non_blocking=True)
+        w_d.copy_(wh, non_blocking=True)
+        if graph_e2e is not None:
+            graph_e2e.replay()
+        else:
+            layers_with_outputs()
+        oh.copy_(out_all, non_blocking=True)
+        stream.synchronize()
+    ms_e2e = timed(step_e2e, max(5, args.steps), 3)
     e2e = {"value": R * L / (ms_e2e / 1e3), "unit": "layer-tokens/s", "ms_per_step": ms_e2e,
            "h2d_bytes_per_step": L * (R * H * 2 + 2 * R * S * 4), "d2h_bytes_per_step": L * R * H * 4,
-           "call": "glmflash_moe_run_host per layer (pinned host input / picks / weights in, output out, sync)"}
+           "call": "per step: pinned host inputs of all layers -> device, glmflash_moe_run per layer (graph replay), all layer "
+                   "outputs -> pinned host, one synchronize"}
+    # the same through the synchronous per-layer host-buffer entry point (glmflash_moe_run_host), N = 1 only
+    if G == 1:
+        def step_layer_calls():
+            for l in range(L):
+                owner(l).run_host(structs[l], xh[l], ph[l], wh[l], R, oh[l], stream=stream)
+        ms_lc = timed(step_layer_calls, max(3, args.steps // 4), 3)
+        e2e["per_layer_host_call"] = {"value": R * L / (ms_lc / 1e3), "ms_per_step": ms_lc,
+                                      "call": "glmflash_moe_run_host per layer: copy in, run, copy out, synchronize"}
 
     # ---- roofline of the dominant kernel: gate/up GEMV alone, every layer, back to back (N = 1 only)
     roofline = None

@@ -101,6 +101,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
     float *part = reinterpret_cast<float *>(wsm);                                // aliases wsm after the K loop
     uint32_t *asm_ = reinterpret_cast<uint32_t *>(wsm + wp);                     // [MATS][SETS*8][AST]
     __shared__ int rows_sh[16];
+    __shared__ float scale_sh[3][128];                                           // epilogue scale vectors of (e, nb)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = lane >> 2, T = lane & 3;
@@ -111,8 +112,28 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
         for (int g = 0; g < NG; ++g) mbar_init(bars + g, 1);
         mbar_fence_init();
     }
-    int cnt, e;
-    if (a.picks) {
+    int cnt = 0, e = -1;
+    if (a.picks && a.rows == 1) {
+        // ---- one row: the distinct experts are the row's picks in ascending order; every warp finds number u itself
+        //      (one load, a few shuffles, no block barrier).  A pick that repeats an earlier slot does not count.
+        if (a.wait_first) pdl_wait();
+        const int pk = lane < a.slots ? __ldcg(a.picks + lane) : 0x7fffffff;
+        bool dup = false;
+        int rank_lt = 0, distinct = 0;
+        for (int j = 0; j < a.slots; ++j) {
+            const int v = __shfl_sync(0xffffffffu, pk, j);
+            bool vdup = false;
+            for (int q = 0; q < j; ++q) vdup |= __shfl_sync(0xffffffffu, pk, q) == v;
+            if (j < lane && v == pk) dup = true;
+            if (!vdup) { distinct++; if (v < pk) rank_lt++; }
+        }
+        const uint32_t hit = __ballot_sync(0xffffffffu, lane < a.slots && !dup && rank_lt == u);
+        cnt = distinct;
+        const int slot = hit ? __ffs(hit) - 1 : 0;
+        e = hit ? __shfl_sync(0xffffffffu, pk, slot) : -1;
+        if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
+        if (tid < 16) rows_sh[tid] = tid == 0 ? slot : -1;
+    } else if (a.picks) {
         // ---- grouping in the CTA: distinct expert number u of the window and its members, from the routing table
         __shared__ uint32_t used_sh[32];
         if (a.wait_first) pdl_wait();
@@ -175,6 +196,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
             const uint32_t *src = T_ + (((size_t)e * KT + kt0 + ktl) * NTILES + (size_t)nb * 8) * 32;
             tma_load_1d(wsm + (size_t)r * GEMV_WROW, src, 1024, bars + (ktl >> 2));
         }
+    }
+    if (tid < 128) {                               // constants of the bank: no dependency on the kernel before
+        const size_t o = (size_t)e * a.N + nb * 128 + tid;
+        scale_sh[0][tid] = __half2float(a.sv0[o]);
+        if (MATS == 2) { scale_sh[1][tid] = __half2float(a.sv1[o]); scale_sh[2][tid] = __half2float(a.sd[o]); }
     }
     pdl_launch_dependents();
     int nmem = 0;
@@ -322,15 +348,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
         fwht128(v0, lane);
         if (MATS == 2) {
             fwht128(v1, lane);
-            const __half *sg = a.sv0 + (size_t)e * a.N + n0, *su = a.sv1 + (size_t)e * a.N + n0,
-                         *sd = a.sd + (size_t)e * a.N + n0;
             float o[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
-                const float gg = fminf(bf16r(v0[j] * HAD_SCALE * __half2float(sg[j])), a.limit);
-                const float uu = fminf(fmaxf(bf16r(v1[j] * HAD_SCALE * __half2float(su[j])), -a.limit), a.limit);
+                const float gg = fminf(bf16r(v0[j] * HAD_SCALE * scale_sh[0][4 * lane + j]), a.limit);
+                const float uu = fminf(fmaxf(bf16r(v1[j] * HAD_SCALE * scale_sh[1][4 * lane + j]), -a.limit), a.limit);
                 const float act = bf16r(bf16r(gg / (1.f + expf(-gg))) * uu);
-                o[j] = act * __half2float(sd[j]);
+                o[j] = act * scale_sh[2][4 * lane + j];
             }
             fwht128(o, lane);
             __half2 h01 = __halves2half2(__float2half_rn(o[0] * HAD_SCALE), __float2half_rn(o[1] * HAD_SCALE));
@@ -338,12 +362,11 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
             uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
             *reinterpret_cast<uint2 *>(a.xd + (size_t)p * a.N + n0) = pk;
         } else {
-            const __half *sv = a.sv0 + (size_t)e * a.N + n0;
             float4 o;
-            o.x = v0[0] * HAD_SCALE * __half2float(sv[0]);
-            o.y = v0[1] * HAD_SCALE * __half2float(sv[1]);
-            o.z = v0[2] * HAD_SCALE * __half2float(sv[2]);
-            o.w = v0[3] * HAD_SCALE * __half2float(sv[3]);
+            o.x = v0[0] * HAD_SCALE * scale_sh[0][4 * lane];
+            o.y = v0[1] * HAD_SCALE * scale_sh[0][4 * lane + 1];
+            o.z = v0[2] * HAD_SCALE * scale_sh[0][4 * lane + 2];
+            o.w = v0[3] * HAD_SCALE * scale_sh[0][4 * lane + 3];
             if (a.mode == GEMV_LINEAR) {
                 __half2 h01 = __halves2half2(__float2half_rn(o.x), __float2half_rn(o.y));
                 __half2 h23 = __halves2half2(__float2half_rn(o.z), __float2half_rn(o.w));
