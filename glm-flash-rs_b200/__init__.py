@@ -75,6 +75,9 @@ SYMBOLS = {
     "glmflash_ep_combine": (_I, [_P, _P, _P, _P, _P, _I, _I]),
     "glmflash_ep_output": (_P, [_P]),
     "glmflash_ep_status": (_P, [_P]),
+    "glmflash_ep_set_wait_limit": (_I, [_P, C.c_uint32]),
+    "glmflash_ep_local_base": (_P, [_P]),
+    "glmflash_ep_connect_ptrs": (_I, [_P, _P]),
 }
 
 _lib = None
@@ -341,7 +344,7 @@ class EpCombine:
         self.cfg, self.rank, self.world = cfg, rank, world
         self._h = C.c_void_p()
         _check(lib().glmflash_ep_new(C.byref(cfg), C.sizeof(cfg), rank, world, C.byref(self._h)))
-        if world > 1:
+        if world > 1 and exchange_handles is not None:
             n = lib().glmflash_ep_handle_bytes()
             buf = C.create_string_buffer(n)
             _check(lib().glmflash_ep_get_handle(self._h, buf))
@@ -363,6 +366,18 @@ class EpCombine:
     def status(self):
         import torch
         return _view(lib().glmflash_ep_status(self._h), (1,), torch.int32)
+
+    @property
+    def local_base(self):
+        return lib().glmflash_ep_local_base(self._h)
+
+    def connect_ptrs(self, bases):
+        """Same-process peers: `bases[k]` = local_base of rank k's owner."""
+        arr = (C.c_void_p * self.world)(*[C.c_void_p(b) for b in bases])
+        _check(lib().glmflash_ep_connect_ptrs(self._h, arr))
+
+    def set_wait_limit(self, polls):
+        _check(lib().glmflash_ep_set_wait_limit(self._h, polls))
 
     def close(self):
         if getattr(self, "_h", None) and self._h.value:

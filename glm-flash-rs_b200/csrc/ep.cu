@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
                                                                 EpPeers peers, unsigned *epoch_ptr, unsigned *done_ptr,
                                                                 int *status, int rank, int world, int rows, int max_rows,
                                                                 int max_ctas, int slots, int H, int E, int shared_exl3,
-                                                                int e_lo, int e_hi) {
+                                                                int e_lo, int e_hi, unsigned wait_polls) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ int ok_sh;
@@ -57,7 +57,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
     if (d < H) {
         for (int s = 0; s < slots; ++s) {
             const int e = picks[r * slots + s];
-            const bool skip = e < 0 || (e >= E ? !shared_exl3 : (e < e_lo || e >= e_hi));
+            const bool skip = e < 0 || e > E || (e == E ? !shared_exl3 : (e < e_lo || e >= e_hi));
             if (skip) continue;
             const float4 y = *reinterpret_cast<const float4 *>(Y + ((size_t)r * slots + s) * H + d);
             if (s == slots - 1) { acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w; }
@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
     if (threadIdx.x < world) {
         const unsigned *f = peers.flags[rank] + ((size_t)par * world + threadIdx.x) * max_ctas + cta;
         bool got = false;
-        for (unsigned i = 0; i < 20000000u; ++i) {
+        for (unsigned i = 0; i < wait_polls; ++i) {
             if (ld_acquire_sys(f) == epoch) { got = true; break; }
             if ((i & 1023u) == 1023u) __nanosleep(200);
         }
@@ -123,6 +123,7 @@ struct glmflash_ep {
     bool opened[EP_MAX_WORLD] = {};
     bool connected = false;
     float *out = nullptr;
+    unsigned wait_polls = 2000000u;               // about a second of polling before a wait gives up
 };
 
 extern "C" size_t glmflash_ep_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
@@ -199,7 +200,28 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
     const dim3 grid((unsigned)((c.hidden / 4 + EP_THREADS - 1) / EP_THREADS), (unsigned)rows);
     return launch_k(ep_combine_kernel, grid, dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w, h->out,
                     peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas, c.slots,
-                    c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi);
+                    c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, h->wait_polls);
+}
+
+extern "C" int glmflash_ep_set_wait_limit(glmflash_ep *h, uint32_t polls) {
+    GF_REQUIRE(h != nullptr && polls > 0, "null argument or zero limit");
+    h->wait_polls = polls;
+    return 0;
+}
+
+// Single-process hosts (one process driving several GPUs with peer access enabled, or a test on one GPU): connect
+// with raw device pointers to the peers' buffers instead of IPC handles.
+extern "C" void *glmflash_ep_local_base(const glmflash_ep *h) { return h ? h->local : nullptr; }
+extern "C" int glmflash_ep_connect_ptrs(glmflash_ep *h, void *const *peer_bases) {
+    GF_REQUIRE(h && peer_bases, "null argument");
+    GF_REQUIRE(!h->connected, "already connected");
+    for (int k = 0; k < h->world; ++k) {
+        if (k == h->rank) continue;
+        GF_REQUIRE(peer_bases[k] != nullptr, "null peer buffer");
+        h->peer_base[k] = peer_bases[k];
+    }
+    h->connected = true;
+    return 0;
 }
 
 extern "C" float *glmflash_ep_output(const glmflash_ep *h) { return h ? h->out : nullptr; }

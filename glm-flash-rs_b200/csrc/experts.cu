@@ -163,14 +163,16 @@ int experts_run_fused(glmflash_experts *e, cudaStream_t s, const glmflash_weight
     a.T0 = w->gt; a.T1 = w->ut;
     a.sv0 = (const __half *)w->svh_g; a.sv1 = (const __half *)w->svh_u; a.sd = (const __half *)w->suh_d;
     a.xd = e->xd; a.y = nullptr; a.K = H; a.N = I; a.mode = GEMV_GATEUP;
+    // down -> y
+    GemvArgs d = a;
+    d.xin = nullptr; d.wait_first = 0; d.suh0 = d.suh1 = nullptr;
+    d.X0 = e->xd; d.X1 = e->xd; d.T0 = w->dt; d.T1 = w->dt;
+    d.sv0 = (const __half *)w->svh_d; d.sv1 = nullptr; d.sd = nullptr;
+    d.xd = nullptr; d.y = e->y; d.K = I; d.N = H; d.mode = GEMV_DOWN;
     if ((e->phases & 2) && launch_gemv(s, 2, a, umax, pdl)) return -1;
     if (!(e->phases & 4)) return 0;
-    // down -> y (the routing table was consumed by the kernel before: it may be read before the dependency wait)
-    a.xin = nullptr; a.wait_first = 0; a.suh0 = a.suh1 = nullptr;
-    a.X0 = e->xd; a.X1 = e->xd; a.T0 = w->dt; a.T1 = w->dt;
-    a.sv0 = (const __half *)w->svh_d; a.sv1 = nullptr; a.sd = nullptr;
-    a.xd = nullptr; a.y = e->y; a.K = I; a.N = H; a.mode = GEMV_DOWN;
-    return launch_gemv(s, 1, a, umax, pdl);
+    // (the routing table was consumed by the kernel before: the down kernel may read it before its dependency wait)
+    return launch_gemv(s, 1, d, umax, pdl);
 }
 }  // namespace gf
 
@@ -271,3 +273,10 @@ extern "C" int glmflash_exl3_linear_static(void *stream, const uint16_t *x, int 
     }
     return glmflash_exl3_linear(stream, x, rows, words, suh, svh, K, N, y, g_static_linear_ptr[dev]);
 }
+
+#ifdef GF_TRACE
+extern "C" int glmflash_trace_set(long long *buffer) {
+    GF_CUDA(cudaMemcpyToSymbol(gf::g_trace, &buffer, sizeof(buffer)));
+    return 0;
+}
+#endif

@@ -4,10 +4,10 @@
 // (native/exl3.cu:59-170,260-321, native/expert_loads.cu:130-285).  Same operands and the same member /
 // pair conventions; a different machine mapping:
 //
-//   * work item = (distinct expert u, 128-column block nb, K split): MATS matrices x 16 k-tiles x 8 n-tiles,
-//     i.e. MATS x 16 contiguous 1-KB rows of packed trellis words.  One elected warp issues them all as TMA
-//     bulk copies (cp.async.bulk) into shared memory at kernel start, four k-tiles per mbarrier, so the whole
-//     item is in flight before anything else happens and the copy engine, not the warps, follows the stream.
+//   * work item = (distinct expert u, 128-column block nb, K split): MATS matrices x KTC k-tiles x 8 n-tiles,
+//     i.e. MATS x KTC contiguous 1-KB rows of packed trellis words.  They are all requested as TMA bulk copies
+//     (cp.async.bulk) into shared memory at kernel start, four k-tiles per mbarrier, so the whole item is in flight
+//     before anything else happens and the copy engine, not the warps, follows the stream.
 //   * a lane reads 16 bytes (4 words of one tile) with one LDS.128: that is 32 weights, all 16 k of two
 //     columns (G, G+8), so only one shuffle per 32 weights is needed for the word that precedes the chunk.
 //     The four lanes of a quad read the same 16-byte slot of four consecutive k-tiles.
@@ -17,8 +17,8 @@
 //   * the weights are the A operand of mma.m16n8k16 (rows = 16 output columns) over a doubled K: the pair
 //     (w, w) meets (x_k, 0), so a.w is accumulated once, in fp32.  Members (<= 8 per set) are the N dimension;
 //     a second set of B operands serves experts with 9..16 members without decoding twice.
-//   * warps of a CTA own disjoint n-tiles (and matrices / K halves), so nothing is reduced across warps by
-//     atomics; the K splits of an (expert, column block) are the CTAs of one thread-block cluster: each leaves its
+//   * warps of a CTA own disjoint n-tiles (and matrices), so nothing is reduced across warps;
+//     the K splits of an (expert, column block) are the CTAs of one thread-block cluster: each leaves its
 //     fp32 partial in its own shared memory, and after a cluster barrier the members are finished by the CTAs
 //     round robin, reading the peers' partials through distributed shared memory and adding them in ascending
 //     split order before the epilogue: Hadamard, scales, SwiGLU, down-input rotation (MATS = 2) or Hadamard and
@@ -34,6 +34,30 @@ namespace gf {
 // native/expert_loads.cu:46-47): 1 = no decode / mma, 2 = no partial exchange and epilogue, 3 = both.
 #ifndef GF_PROBE
 #define GF_PROBE 0
+#endif
+// GF_TRACE (timing experiments only): thread 0 of every CTA stamps the global nanosecond timer at the phase boundaries
+// into a buffer registered with glmflash_trace_set(): [MATS - 1][(u * splits + split) * 16 + nb (< 16384)][16] int64.
+#ifdef GF_TRACE
+static __device__ long long *g_trace = nullptr;    // one copy per translation unit; experts.cu owns the used one
+#define GF_STAMP(i)                                                                                              \
+    do {                                                                                                         \
+        if (threadIdx.x == 0 && g_trace) {                                                                       \
+            long long t_;                                                                                        \
+            asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t_));                                                \
+            g_trace[(((size_t)(MATS - 1) * 16384 + ((size_t)(u * gridDim.y + split) * 16 + nb)) << 4) + (i)] = t_; \
+        }                                                                                                        \
+    } while (0)
+#define GF_STAMP_SMID(i)                                                                                         \
+    do {                                                                                                         \
+        if (threadIdx.x == 0 && g_trace) {                                                                       \
+            unsigned t_;                                                                                         \
+            asm volatile("mov.u32 %0, %smid;" : "=r"(t_));                                                       \
+            g_trace[(((size_t)(MATS - 1) * 16384 + ((size_t)(u * gridDim.y + split) * 16 + nb)) << 4) + (i)] = t_; \
+        }                                                                                                        \
+    } while (0)
+#else
+#define GF_STAMP(i) do { } while (0)
+#define GF_STAMP_SMID(i) do { } while (0)
 #endif
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_MAX_SPLITS = 8;                 // K splits of an item = CTAs of a cluster (portable maximum)
@@ -61,9 +85,20 @@ struct GemvArgs {
     int rows, x_stride, wait_first;
 };
 
+// Position of the n-th (0-based) set bit of w (which has more than n set bits): five popcount steps.
+__device__ __forceinline__ int nth_set_bit(uint32_t w, int n) {
+    int pos = 0;
+#pragma unroll
+    for (int width = 16; width >= 1; width >>= 1) {
+        const int c = __popc(w & ((1u << width) - 1u));
+        if (n >= c) { n -= c; w >>= width; pos += width; }
+    }
+    return pos;
+}
+
 __device__ __forceinline__ bool expert_skipped(int e, int E, int shared_exl3, int e_lo, int e_hi) {
     // the window [e_lo, e_hi) selects routed experts; the shared expert (id E) is governed by shared_exl3 alone
-    return e < 0 || (e >= E ? !shared_exl3 : (e < e_lo || e >= e_hi));
+    return e < 0 || e > E || (e == E ? !shared_exl3 : (e < e_lo || e >= e_hi));
 }
 
 // (w, w) from a masked codeword: one half-precision add of its two halves.
@@ -82,21 +117,23 @@ inline void gemv_split(int K, int &ktc, int &sk) {
 // dynamic shared memory size of a launch
 inline size_t gemv_smem_bytes(int mats, int sets, int ktc) {
     size_t w = (size_t)mats * ktc * GEMV_WROW;
-    size_t part = (size_t)2 * sets * 8 * GEMV_PST * sizeof(float);
-    size_t a = (size_t)mats * sets * 8 * (ktc * 16 + 8) * 4;
+    size_t part = (size_t)mats * sets * 8 * GEMV_PST * sizeof(float);
+    size_t a = sets == 2 ? (size_t)mats * sets * 8 * (ktc * 8 + 4) * 4 : (size_t)mats * sets * 8 * (ktc * 16 + 8) * 4;
     return 128 + (w > part ? w : part) + a;
 }
 
-// Work item (cluster) = (distinct expert u, 128-column block nb); CTA r of the cluster owns K split r: MATS x KTC rows
-// of 1 KB.  8 warps.  MATS = 2: warp = (matrix, pair of n-tiles), all k groups.  MATS = 1: warp = (K half, pair).
+// Work item (cluster) = (distinct expert u, 128-column block nb); CTA `split` of the cluster owns K split `split`:
+// MATS x KTC rows of 1 KB.  8 warps.  MATS = 2: warp = (matrix, pair of n-tiles).  MATS = 1: warp = n-tile.
+// Returns 0 after a computed item, 1 when u is beyond the distinct experts of the window, 2 when the expert is outside
+// this rank's window.
 template <int MATS, int SETS>
-__global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(const GemvArgs a) {
-    extern __shared__ __align__(128) unsigned char smem[];
+__device__ __forceinline__ int gemv_item(const GemvArgs &a, unsigned char *smem, const int nb, const int split, const int u) {
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);                         // one barrier per 4 k-tiles (<= 16)
     unsigned char *wsm = smem + 128;                                             // [MATS][KTC] rows of GEMV_WROW
-    const int KTC = a.KTC, NG = KTC >> 2, KC = KTC * 16, AST = KC + 8;
+    constexpr bool PACKED = SETS == 2;               // layout of the staged activations, see below
+    const int KTC = a.KTC, NG = KTC >> 2, KC = KTC * 16, AST = PACKED ? (KC >> 1) + 4 : KC + 8;   // dwords per member row
     const size_t wbytes = (size_t)MATS * KTC * GEMV_WROW;
-    constexpr size_t PBYTES = (size_t)2 * SETS * 8 * GEMV_PST * sizeof(float);
+    constexpr size_t PBYTES = (size_t)MATS * SETS * 8 * GEMV_PST * sizeof(float);
     const size_t wp = wbytes > PBYTES ? wbytes : PBYTES;
     float *part = reinterpret_cast<float *>(wsm);                                // aliases wsm after the K loop
     uint32_t *asm_ = reinterpret_cast<uint32_t *>(wsm + wp);                     // [MATS][SETS*8][AST]
@@ -105,18 +142,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = lane >> 2, T = lane & 3;
-    const int nb = blockIdx.x, split = blockIdx.y, u = blockIdx.z;               // split == rank in the cluster
     const int KT = a.K >> 4, NTILES = a.N >> 4;
 
+    GF_STAMP(0);
     if (tid == 0) {
-        for (int g = 0; g < NG; ++g) mbar_init(bars + g, 1);
+        for (int g = 0; g < NG; ++g) {
+            mbar_init(bars + g, 1);
+            mbar_expect_tx(bars + g, MATS * 4 * 1024);   // the one arrival; the copies below complete the byte count
+        }
         mbar_fence_init();
     }
+    if (a.wait_first) pdl_wait();                   // the routing table / layer input may belong to the kernel before
+    GF_STAMP_SMID(13);
     int cnt = 0, e = -1;
     if (a.picks && a.rows == 1) {
         // ---- one row: the distinct experts are the row's picks in ascending order; every warp finds number u itself
         //      (one load, a few shuffles, no block barrier).  A pick that repeats an earlier slot does not count.
-        if (a.wait_first) pdl_wait();
         const int pk = lane < a.slots ? __ldcg(a.picks + lane) : 0x7fffffff;
         bool dup = false;
         int rank_lt = 0, distinct = 0;
@@ -128,21 +169,22 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
             if (!vdup) { distinct++; if (v < pk) rank_lt++; }
         }
         const uint32_t hit = __ballot_sync(0xffffffffu, lane < a.slots && !dup && rank_lt == u);
+        GF_STAMP(14);
         cnt = distinct;
         const int slot = hit ? __ffs(hit) - 1 : 0;
         e = hit ? __shfl_sync(0xffffffffu, pk, slot) : -1;
-        if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
+        if (u >= cnt) return 1;                                // uniform for the whole cluster
+        if (expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return 2;
         if (tid < 16) rows_sh[tid] = tid == 0 ? slot : -1;
     } else if (a.picks) {
         // ---- grouping in the CTA: distinct expert number u of the window and its members, from the routing table
         __shared__ uint32_t used_sh[32];
-        if (a.wait_first) pdl_wait();
         if (tid < 32) used_sh[tid] = 0u;
         __syncthreads();
         const int np = a.rows * a.slots;
         for (int i = tid; i < np; i += GEMV_THREADS) {
             const int pk = __ldcg(a.picks + i);
-            if ((unsigned)pk < 1024u) atomicOr(&used_sh[pk >> 5], 1u << (pk & 31));
+            if (pk >= 0 && pk <= a.E) atomicOr(&used_sh[pk >> 5], 1u << (pk & 31));   // ids above E name nothing
         }
         __syncthreads();
         __shared__ int e_sh, cnt_sh;
@@ -157,12 +199,13 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
             }
             const int excl = incl - c;
             if (lane == 31) cnt_sh = incl;
-            if (u >= excl && u < incl) e_sh = lane * 32 + (int)__fns(bts, 0, u - excl + 1);
+            if (u >= excl && u < incl) e_sh = lane * 32 + nth_set_bit(bts, u - excl);
             if (lane == 31 && u >= incl) e_sh = -1;
         }
         __syncthreads();
         e = e_sh; cnt = cnt_sh;
-        if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
+        if (u >= cnt) return 1;                                // uniform for the whole cluster
+        if (expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return 2;
         if (warp == 0) {                                       // rows <= 16: one lane per row, ascending row order
             int slot = -1;
             if (lane < a.rows)
@@ -179,67 +222,100 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
         e = __ldcg(a.ids + u);
         int code = -1;
         if (tid < 16 && tid < a.maxm) code = __ldcg(a.members + (size_t)u * a.maxm + tid);
-        if (u >= cnt || expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return;   // uniform for the whole cluster
+        if (u >= cnt) return 1;                                // uniform for the whole cluster
+        if (expert_skipped(e, a.E, a.shared_exl3, a.e_lo, a.e_hi)) return 2;
         if (tid < 16) rows_sh[tid] = code >= 0 ? (code >> 5) * a.slots + (code & 31) : -1;
     }
+    GF_STAMP(15);
     __syncthreads();
+    GF_STAMP(1);
 
-    // ---- the whole item's packed words, in flight at once
-    const int kt0 = split * KTC;
-    if (warp == 0) {
-        if (lane == 0)
-            for (int g = 0; g < NG; ++g) mbar_expect_tx(bars + g, MATS * 4 * 1024);
-        __syncwarp();
-        for (int r = lane; r < MATS * KTC; r += 32) {
+    int nmem = 0;
+#pragma unroll
+    for (int m = 0; m < SETS * 8; ++m) nmem += rows_sh[m] >= 0;   // members come first
+    const int kt0 = split * KTC, k0 = kt0 * 16;
+
+    // ---- small operands first: the scale vectors of (e, nb) and the first rotation item of every warp are requested
+    //      BEFORE the weight stream, so that they do not queue behind it in the memory system
+    unsigned short sc0 = 0, sc1 = 0, sc2 = 0;      // raw fp16 bits; converted where they are stored, after the rotation
+    if (tid < 128) {                               // constants of the bank: no dependency on the kernel before
+        const size_t o = (size_t)e * a.N + nb * 128 + tid;
+        sc0 = __ldg(reinterpret_cast<const unsigned short *>(a.sv0) + o);
+        if (MATS == 2) {
+            sc1 = __ldg(reinterpret_cast<const unsigned short *>(a.sv1) + o);
+            sc2 = __ldg(reinterpret_cast<const unsigned short *>(a.sd) + o);
+        }
+    }
+    // rotation items (xin path): one warp per (matrix, member, 128-block of this K range)
+    const int blocks = KC >> 7;
+    const int rot_items = a.xin ? MATS * nmem * blocks : 0;
+    uint2 rot_x = make_uint2(0u, 0u), rot_s = make_uint2(0u, 0u);
+    auto rot_load = [&](int it) {
+        const int blk = it % blocks, mm = it / blocks;
+        const int m = mm % nmem, mat = mm / nmem;
+        const int row = rows_sh[m] / a.slots;
+        const int kl = blk * 128 + 4 * lane;
+        rot_x = __ldcg(reinterpret_cast<const uint2 *>(a.xin + (size_t)row * a.x_stride + k0 + kl));
+        rot_s = __ldg(reinterpret_cast<const uint2 *>((mat ? a.suh1 : a.suh0) + (size_t)e * a.K + k0 + kl));
+    };
+    const bool rot_early = a.wait_first != 0 && warp < rot_items;   // x is complete only after the dependency wait
+    if (rot_early) rot_load(warp);
+
+    // ---- the whole item's packed words, in flight at once, the requests spread over the warps (an issuing thread is
+    //      held while the copy engine accepts its request)
+    {
+        constexpr int WARPS = GEMV_THREADS / 32;
+        const int per_warp = (MATS * KTC + WARPS - 1) / WARPS;
+        const int r = warp * per_warp + lane;
+        if (lane < per_warp && r < MATS * KTC) {
             const int mat = r / KTC, ktl = r % KTC;
             const uint32_t *T_ = mat ? a.T1 : a.T0;
             const uint32_t *src = T_ + (((size_t)e * KT + kt0 + ktl) * NTILES + (size_t)nb * 8) * 32;
             tma_load_1d(wsm + (size_t)r * GEMV_WROW, src, 1024, bars + (ktl >> 2));
         }
     }
-    if (tid < 128) {                               // constants of the bank: no dependency on the kernel before
-        const size_t o = (size_t)e * a.N + nb * 128 + tid;
-        scale_sh[0][tid] = __half2float(a.sv0[o]);
-        if (MATS == 2) { scale_sh[1][tid] = __half2float(a.sv1[o]); scale_sh[2][tid] = __half2float(a.sd[o]); }
-    }
     pdl_launch_dependents();
-    int nmem = 0;
-#pragma unroll
-    for (int m = 0; m < SETS * 8; ++m) nmem += rows_sh[m] >= 0;   // members come first
+    GF_STAMP(2);
+    bool ok = true;
     pdl_wait();                                   // X belongs to the kernel before this one (no-op after wait_first)
+    GF_STAMP(3);
 
-    // ---- stage the members' activations of this K range as (x_k, 0) pairs, permuted to the mma order:
-    //      dword position of local k = 64 g + 16 T + 8 h + 2 t + b  is  g*64 + (2t + h)*8 + 2T + b.
-    //      Rows of absent members are left as they are: an mma column depends on its own B column only, and the
-    //      columns of absent members are never stored.
+    // ---- stage the members' activations of this K range, one row of AST dwords per member.
+    //      PACKED (two member sets): fp16, natural k order (AST = KC / 2 + 4 keeps the 16-byte reads of the K loop free
+    //      of bank conflicts); the (x_k, 0) operand pairs are cut in the K loop.  This halves the staging area, which is
+    //      what lets four CTAs share an SM.
+    //      Otherwise (one set): ready-made (x_k, 0) dword pairs, permuted to the mma order: the pair of local
+    //      k = 64 g + 16 T + 8 h + 2 t + b sits at dword g*64 + (2t + h)*8 + 2T + b.
     auto stage_pos = [](int kl) {
         const int g = kl >> 6, TT = (kl >> 4) & 3, h = (kl >> 3) & 1, t = (kl >> 1) & 3;
         return g * 64 + (2 * t + h) * 8 + 2 * TT;
     };
-    const int k0 = kt0 * 16;
+    //      Rows of absent members are left as they are: an mma column depends on its own B column only, and the
+    //      columns of absent members are never stored.
     if (a.xin) {
-        // rotate the layer input here (upstream rot_in_kernel, native/exl3.cu:224-241): one warp per (matrix, member,
-        // 128-block of this K range): fp16(H(x * suh) / sqrt 128), the same butterflies and rounding as the kernel form
-        const int blocks = KC >> 7;
-        for (int it = warp; it < MATS * nmem * blocks; it += GEMV_THREADS / 32) {
+        // rotate the layer input here (upstream rot_in_kernel, native/exl3.cu:224-241):
+        // fp16(H(x * suh) / sqrt 128), the same butterflies and rounding as the kernel form
+        for (int it = warp; it < rot_items; it += GEMV_THREADS / 32) {
+            if (!(rot_early && it == warp)) rot_load(it);
             const int blk = it % blocks, mm = it / blocks;
             const int m = mm % nmem, mat = mm / nmem;
-            const int row = rows_sh[m] / a.slots;
             const int kl = blk * 128 + 4 * lane;
-            const uint2 xv = __ldcg(reinterpret_cast<const uint2 *>(a.xin + (size_t)row * a.x_stride + k0 + kl));
-            const uint2 sv = __ldg(reinterpret_cast<const uint2 *>((mat ? a.suh1 : a.suh0) + (size_t)e * a.K + k0 + kl));
-            const __nv_bfloat162 x01 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.x),
-                                 x23 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.y);
-            const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv.x), s23 = *reinterpret_cast<const __half2 *>(&sv.y);
+            const __nv_bfloat162 x01 = *reinterpret_cast<const __nv_bfloat162 *>(&rot_x.x),
+                                 x23 = *reinterpret_cast<const __nv_bfloat162 *>(&rot_x.y);
+            const __half2 s01 = *reinterpret_cast<const __half2 *>(&rot_s.x), s23 = *reinterpret_cast<const __half2 *>(&rot_s.y);
             float v[4] = {__bfloat162float(x01.x) * __low2float(s01), __bfloat162float(x01.y) * __high2float(s01),
                           __bfloat162float(x23.x) * __low2float(s23), __bfloat162float(x23.y) * __high2float(s23)};
             fwht128(v, lane);
-            uint32_t r[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) r[j] = (uint32_t)__half_as_ushort(__float2half_rn(v[j] * HAD_SCALE));
+            const __half2 r01 = __halves2half2(__float2half_rn(v[0] * HAD_SCALE), __float2half_rn(v[1] * HAD_SCALE));
+            const __half2 r23 = __halves2half2(__float2half_rn(v[2] * HAD_SCALE), __float2half_rn(v[3] * HAD_SCALE));
+            const uint32_t w01 = *reinterpret_cast<const uint32_t *>(&r01), w23 = *reinterpret_cast<const uint32_t *>(&r23);
             uint32_t *dst = asm_ + ((size_t)mat * SETS * 8 + m) * AST;
-            *reinterpret_cast<uint2 *>(dst + stage_pos(kl)) = make_uint2(r[0], r[1]);
-            *reinterpret_cast<uint2 *>(dst + stage_pos(kl + 2)) = make_uint2(r[2], r[3]);
+            if (PACKED) {
+                *reinterpret_cast<uint2 *>(dst + (kl >> 1)) = make_uint2(w01, w23);
+            } else {
+                *reinterpret_cast<uint2 *>(dst + stage_pos(kl)) = make_uint2(w01 & 0xffffu, w01 >> 16);
+                *reinterpret_cast<uint2 *>(dst + stage_pos(kl + 2)) = make_uint2(w23 & 0xffffu, w23 >> 16);
+            }
         }
     } else {
         const int half = KC >> 1;
@@ -249,40 +325,58 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
             const int m = mm % nmem, mat = mm / nmem;
             const int p = rows_sh[m];
             const uint32_t v = __ldcg(reinterpret_cast<const uint32_t *>((mat ? a.X1 : a.X0) + (size_t)p * a.K + k0) + kp);
-            *reinterpret_cast<uint2 *>(asm_ + ((size_t)mat * SETS * 8 + m) * AST + stage_pos(2 * kp)) =
-                make_uint2(v & 0xffffu, v >> 16);
+            uint32_t *dst = asm_ + ((size_t)mat * SETS * 8 + m) * AST;
+            if (PACKED) dst[kp] = v;
+            else *reinterpret_cast<uint2 *>(dst + stage_pos(2 * kp)) = make_uint2(v & 0xffffu, v >> 16);
+        }
+    }
+    if (tid < 128) {
+        scale_sh[0][tid] = __half2float(__ushort_as_half(sc0));
+        if (MATS == 2) {
+            scale_sh[1][tid] = __half2float(__ushort_as_half(sc1));
+            scale_sh[2][tid] = __half2float(__ushort_as_half(sc2));
         }
     }
     __syncthreads();
+    GF_STAMP(4);
 
-    // ---- K loop
-    const int sub = warp >> 2, ntp = warp & 3;
-    const int mat = MATS == 2 ? sub : 0;
-    const int g_begin = MATS == 2 ? 0 : sub * (NG >> 1), g_end = MATS == 2 ? NG : (sub + 1) * (NG >> 1);
+    // ---- K loop.  MATS = 2: warp = (matrix, n-tiles 2 ntp, 2 ntp + 1);  MATS = 1: warp = n-tile.
+    constexpr int NPW = MATS == 2 ? 2 : 1;
+    const int mat = MATS == 2 ? warp >> 2 : 0;
+    const int nt0 = MATS == 2 ? (warp & 3) * 2 : warp;
     const bool two_sets = SETS == 2 && nmem > 8;
-    float acc[2][SETS][4];
+    float acc[NPW][SETS][4];
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
+    for (int n = 0; n < NPW; ++n)
 #pragma unroll
         for (int s = 0; s < SETS; ++s)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[n][s][c] = 0.f;
 
-    bool ok = true;
 #pragma unroll 1
-    for (int g = g_begin; g < g_end; ++g) {
-        // B operands of the group's 8 mma: (x, 0) pairs of member G (set 0) and member 8 + G (set 1)
-        uint2 b[SETS][8];
+    for (int g = 0; g < NG; ++g) {
+        // B operands of the group's 8 mma: the 16 activations k = 64 g + 16 T .. + 15 of member G (set 0) and member
+        // 8 + G (set 1).  mma number 2t + h takes (x_k, 0), (x_k+1, 0) with k = 64 g + 16 T + 8 h + 2 t.
+        uint32_t bp[SETS][8];                       // PACKED: word 4h + t holds (x_k, x_k+1)
+        uint2 b1[8];                                // otherwise: entry 2t + h holds the two ready operands
+        if (PACKED) {
 #pragma unroll
-        for (int s = 0; s < SETS; ++s) {
-            const uint32_t *ar = asm_ + ((size_t)mat * SETS * 8 + s * 8 + G) * AST + g * 64 + 2 * T;
+            for (int s = 0; s < SETS; ++s) {
+                const uint4 *ar = reinterpret_cast<const uint4 *>(asm_ + ((size_t)mat * SETS * 8 + s * 8 + G) * AST + g * 32 + 8 * T);
+                const uint4 lo = ar[0], hi = ar[1];
+                bp[s][0] = lo.x; bp[s][1] = lo.y; bp[s][2] = lo.z; bp[s][3] = lo.w;
+                bp[s][4] = hi.x; bp[s][5] = hi.y; bp[s][6] = hi.z; bp[s][7] = hi.w;
+            }
+        } else {
+            const uint32_t *ar = asm_ + ((size_t)mat * SETS * 8 + G) * AST + g * 64 + 2 * T;
 #pragma unroll
-            for (int m = 0; m < 8; ++m) b[s][m] = *reinterpret_cast<const uint2 *>(ar + m * 8);
+            for (int m = 0; m < 8; ++m) b1[m] = *reinterpret_cast<const uint2 *>(ar + m * 8);
         }
         if (!mbar_wait(bars + g, 0)) { ok = false; break; }
-        const unsigned char *wrow = wsm + ((size_t)mat * KTC + 4 * g + T) * GEMV_WROW + ntp * 256 + G * 16;
+        if (g == 0) GF_STAMP(5);
+        const unsigned char *wrow = wsm + ((size_t)mat * KTC + 4 * g + T) * GEMV_WROW + nt0 * 128 + G * 16;
 #pragma unroll
-        for (int n = 0; n < ((GF_PROBE & 1) ? 0 : 2); ++n) {
+        for (int n = 0; n < ((GF_PROBE & 1) ? 0 : NPW); ++n) {
             const uint4 wv = *reinterpret_cast<const uint4 *>(wrow + n * 128);
             const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
             const uint32_t before = __shfl_sync(0xffffffffu, wv.w, (lane + 28) & 31);   // word 4G-1 (circular)
@@ -300,51 +394,71 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
                     codeword_pair(uu[2 * h], x0, x1);        // k = 2t + 8h:     columns G, G + 8
                     codeword_pair(uu[2 * h + 1], x2, x3);    // k = 2t + 8h + 1: columns G, G + 8
                     af[0] = weight_dup(x0); af[1] = weight_dup(x1); af[2] = weight_dup(x2); af[3] = weight_dup(x3);
-                    const int m = 2 * t + h;
-                    mma16816(acc[n][0], af, b[0][m].x, b[0][m].y);
-                    if (SETS == 2 && two_sets) mma16816(acc[n][SETS - 1], af, b[SETS - 1][m].x, b[SETS - 1][m].y);
+                    if (!PACKED) {
+                        mma16816(acc[n][0], af, b1[2 * t + h].x, b1[2 * t + h].y);
+                    } else {
+                        const uint32_t bw0 = bp[0][4 * h + t];
+                        mma16816(acc[n][0], af, bw0 & 0xffffu, bw0 >> 16);
+                    }
+                    if (SETS == 2 && two_sets) {
+                        const uint32_t bw1 = bp[SETS - 1][4 * h + t];
+                        mma16816(acc[n][SETS - 1], af, bw1 & 0xffffu, bw1 >> 16);
+                    }
                 }
             }
         }
     }
     if (!ok && lane == 0) atomicExch(a.status, GF_STATUS_TMA_TIMEOUT);
     if (GF_PROBE & 2) {
-        if (acc[0][0][0] == 123.f) a.y[0] = acc[1][0][1];
-        return;
+        if (acc[0][0][0] == 123.f) a.y[0] = acc[NPW - 1][0][1];
+        return 0;
     }
+    GF_STAMP(6);
     __syncthreads();                                // wsm is dead: part aliases it
+    GF_STAMP(7);
 
-    // ---- this split's partial[sub][member][column] in shared memory, visible to the cluster
+    // ---- this split's partial[matrix][member][column] in shared memory, visible to the cluster
 #pragma unroll
-    for (int n = 0; n < 2; ++n)
+    for (int n = 0; n < NPW; ++n)
 #pragma unroll
         for (int s = 0; s < SETS; ++s) {
-            const int col = (ntp * 2 + n) * 16 + G, mem = s * 8 + 2 * T;
-            float *pp = part + ((size_t)sub * SETS * 8 + mem) * GEMV_PST + col;
+            const int col = (nt0 + n) * 16 + G, mem = s * 8 + 2 * T;
+            float *pp = part + ((size_t)mat * SETS * 8 + mem) * GEMV_PST + col;
             pp[0] = acc[n][s][0];
             pp[GEMV_PST] = acc[n][s][1];
             pp[8] = acc[n][s][2];
             pp[GEMV_PST + 8] = acc[n][s][3];
         }
     cluster_sync();
+    GF_STAMP(8);
 
     // ---- member m is finished by CTA m % SK: the splits' partials are read from the peers' shared memory and added
-    //      in split order (for one matrix: K half 0 then 1 inside a split), then the epilogue runs in the warp.
+    //      in split order, then the epilogue runs in the warp.
     for (int m = split + a.SK * warp; m < nmem; m += a.SK * (GEMV_THREADS / 32)) {
         const int p = rows_sh[m];
         const int n0 = nb * 128 + 4 * lane;
         float v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int s = 0; s < a.SK; ++s) {
-            const float *rp = cluster_map(part, s) + (size_t)m * GEMV_PST + 4 * lane;
-            const float4 q = *reinterpret_cast<const float4 *>(rp);
-            const float4 r = *reinterpret_cast<const float4 *>(rp + (size_t)SETS * 8 * GEMV_PST);
-            if (MATS == 2) {
-                v0[0] += q.x; v0[1] += q.y; v0[2] += q.z; v0[3] += q.w;
-                v1[0] += r.x; v1[1] += r.y; v1[2] += r.z; v1[3] += r.w;
-            } else {
-                v0[0] += q.x + r.x; v0[1] += q.y + r.y; v0[2] += q.z + r.z; v0[3] += q.w + r.w;
-            }
+        // the splits' partials, four splits per round trip through the cluster's shared memory (all reads of a batch are
+        // issued before its first add); the adds keep the ascending split order
+#pragma unroll
+        for (int s0 = 0; s0 < GEMV_MAX_SPLITS; s0 += 4) {
+            if (s0 >= a.SK) break;
+            float4 q[4], r[4];
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s0 + s < a.SK) {
+                    const float *rp = cluster_map(part, s0 + s) + (size_t)m * GEMV_PST + 4 * lane;
+                    q[s] = *reinterpret_cast<const float4 *>(rp);
+                    if (MATS == 2) r[s] = *reinterpret_cast<const float4 *>(rp + (size_t)SETS * 8 * GEMV_PST);
+                }
+#pragma unroll
+            for (int s = 0; s < 4; ++s)
+                if (s0 + s < a.SK) {
+                    v0[0] += q[s].x; v0[1] += q[s].y; v0[2] += q[s].z; v0[3] += q[s].w;
+                    if (MATS == 2) { v1[0] += r[s].x; v1[1] += r[s].y; v1[2] += r[s].z; v1[3] += r[s].w; }
+                }
         }
+        GF_STAMP(11);
         fwht128(v0, lane);
         if (MATS == 2) {
             fwht128(v1, lane);
@@ -356,6 +470,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
                 const float act = bf16r(bf16r(gg / (1.f + expf(-gg))) * uu);
                 o[j] = act * scale_sh[2][4 * lane + j];
             }
+            GF_STAMP(12);
             fwht128(o, lane);
             __half2 h01 = __halves2half2(__float2half_rn(o[0] * HAD_SCALE), __float2half_rn(o[1] * HAD_SCALE));
             __half2 h23 = __halves2half2(__float2half_rn(o[2] * HAD_SCALE), __float2half_rn(o[3] * HAD_SCALE));
@@ -377,7 +492,19 @@ __global__ void __launch_bounds__(GEMV_THREADS, SETS == 1 ? 4 : 3) gemv_kernel(c
             }
         }
     }
+    GF_STAMP(9);
     cluster_sync();                                 // peers may still be reading this CTA's partials
+    GF_STAMP(10);
+    return 0;
+}
+
+// One item per cluster: grid (N / 128, SK, distinct-expert bound), cluster (1, SK, 1).  (A persistent form, in which a
+// resident set of clusters walks the item list, measured slower: clusters that start together stay in lock step, so
+// the fetch, decode and exchange phases of the CTAs sharing an SM stop overlapping.)
+template <int MATS, int SETS>
+__global__ void __launch_bounds__(GEMV_THREADS, 4) gemv_kernel(const GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    gemv_item<MATS, SETS>(a, smem, blockIdx.x, blockIdx.y, blockIdx.z);
 }
 
 // Input rotation (upstream rot_in_kernel, native/exl3.cu:224-241): one warp per (pair, 128-block, matrix);

@@ -19,20 +19,39 @@ int experts_run_fused(glmflash_experts *e, cudaStream_t s, const glmflash_weight
 __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
                                                       const float *__restrict__ route_w, float *__restrict__ out, int rows,
                                                       int slots, int H, int E, int shared_exl3, int e_lo, int e_hi) {
-    pdl_wait();
-    pdl_launch_dependents();
+    // The routing table and the weights were complete before the expert kernels ran (those read them), so they are
+    // fetched ahead of the dependency wait; only the pair results Y belong to the kernel in front.
     const int r = blockIdx.y;
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    __shared__ float wgt_sh[32];
+    __shared__ uint32_t live_sh;
+    if (threadIdx.x < 32) {
+        const int s = threadIdx.x;
+        bool keep = false;
+        float w = 0.f;
+        if (s < slots) {
+            const int e = picks[r * slots + s];
+            keep = !(e < 0 || e > E || (e == E ? !shared_exl3 : (e < e_lo || e >= e_hi)));
+            w = route_w[r * slots + s];
+        }
+        wgt_sh[s] = w;
+        const uint32_t mask = __ballot_sync(0xffffffffu, keep);
+        if (s == 0) live_sh = mask;
+    }
+    __syncthreads();
+    const uint32_t live = live_sh;
+    pdl_wait();
+    pdl_launch_dependents();
     if (d >= H) return;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s = 0; s < slots; ++s) {
-        const int e = picks[r * slots + s];
-        const bool skip = e < 0 || (e >= E ? !shared_exl3 : (e < e_lo || e >= e_hi));
-        if (skip) continue;
-        const float w = s == slots - 1 ? 1.f : route_w[r * slots + s];
+        if (!((live >> s) & 1u)) continue;
         const float4 y = *reinterpret_cast<const float4 *>(Y + ((size_t)r * slots + s) * H + d);
         if (s == slots - 1) { acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w; }
-        else { acc.x += w * y.x; acc.y += w * y.y; acc.z += w * y.z; acc.w += w * y.w; }
+        else {
+            const float w = wgt_sh[s];
+            acc.x += w * y.x; acc.y += w * y.y; acc.z += w * y.z; acc.w += w * y.w;
+        }
     }
     *reinterpret_cast<float4 *>(out + (size_t)r * H + d) = acc;
 }

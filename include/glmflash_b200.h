@@ -202,6 +202,12 @@ int  glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y, const int
                          int shared_here);
 float *glmflash_ep_output(const glmflash_ep *h);
 const int32_t *glmflash_ep_status(const glmflash_ep *h);
+/* Number of polls after which a wait for a peer gives up (default 2,000,000, about a second). */
+int  glmflash_ep_set_wait_limit(glmflash_ep *h, uint32_t polls);
+/* For a host that drives several GPUs from ONE process (peer access enabled by the host): connect with the peers'
+ * glmflash_ep_local_base() pointers instead of IPC handles. */
+void *glmflash_ep_local_base(const glmflash_ep *h);
+int  glmflash_ep_connect_ptrs(glmflash_ep *h, void *const *peer_bases /* world entries, own entry ignored */);
 /* out[r][:] = sum over ranks (ascending rank order) of gathered[rank][r][:], the fixed-order sum upstream
  * applies after its all-gather (src/model.rs:485-496, src/comm.rs:1-2).  gathered: fp32 [world][rows][H]. */
 int glmflash_rank_sum(void *stream, const float *gathered, int world, int rows, int hidden, float *out);

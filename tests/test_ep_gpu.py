@@ -81,3 +81,42 @@ def test_ep_two_gpus(cuda):
         for rows, l, same, err in res:
             assert same, (rank, rows, l, "ranks disagree")
             assert err < 1e-5, (rank, rows, l, err)
+
+
+def test_peer_that_never_arrives_times_out(pkg, synth, cuda):
+    """Failure detection without a fault: two owners (ranks 0 and 1 of a world of 2) live on ONE GPU and are connected
+    by pointers; only rank 0 calls the exchange, so its wait for rank 1's flag runs out after the (shortened) poll
+    limit.  The kernel returns, the status word says PEER_TIMEOUT, and the context stays usable: once rank 1 does
+    arrive for that epoch, a later pair of calls completes and gives the sum."""
+    import torch
+    rows = 2
+    cfgs = [pkg.make_config(H, I, E, S, max_rows=rows, shared_exl3=0, expert_lo=r * 32, expert_hi=(r + 1) * 32, pdl=0) for r in (0, 1)]
+    eps = [pkg.EpCombine(cfgs[r], r, 2, None) for r in (0, 1)]
+    bases = [e.local_base for e in eps]
+    for e in eps:
+        e.connect_ptrs(bases)
+        e.set_wait_limit(20000)
+    picks, rw = synth.route(5, rows, E, S - 1)
+    pd, wd = torch.from_numpy(picks).to(cuda), torch.from_numpy(rw).to(cuda)
+    Y = torch.randn((rows * S, H), dtype=torch.float32, device=cuda)
+    eps[0].combine(C_void(Y), pd, wd, rows, True)
+    torch.cuda.synchronize()
+    assert int(eps[0].status.cpu()[0]) == 4                     # GF_STATUS_PEER_TIMEOUT
+    # the context is alive and the protocol recovers: rank 1 delivers the missed epoch, then both run a fresh one
+    eps[1].combine(C_void(Y), pd, wd, rows, False)
+    torch.cuda.synchronize()
+    eps[0].status.zero_()
+    eps[0].set_wait_limit(2000000)
+    eps[1].set_wait_limit(20000)
+    eps[1].combine(C_void(Y), pd, wd, rows, False)               # rank 1 pushes epoch 2 (its own wait for rank 0 runs out)
+    eps[0].combine(C_void(Y), pd, wd, rows, True)                # rank 0 finds rank 1's epoch-2 partial already there
+    torch.cuda.synchronize()
+    assert int(eps[0].status.cpu()[0]) == 0
+    y = Y.view(rows, S, H)
+    want = (wd[:, :, None] * y).sum(1)
+    assert torch.allclose(eps[0].output[:rows], want, rtol=1e-5, atol=1e-5)
+
+
+def C_void(t):
+    import ctypes
+    return ctypes.c_void_p(t.data_ptr())
