@@ -43,7 +43,7 @@ int launch_kc(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, siz
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = smem;
     cfg.stream = s;
-    cudaLaunchAttribute at[2];
+    cudaLaunchAttribute at[3];
     int n = 0;
     if (pdl) {
         at[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -55,6 +55,10 @@ int launch_kc(void (*kernel)(KArgs...), dim3 grid, dim3 block, dim3 cluster, siz
         at[n].val.clusterDim.x = cluster.x;
         at[n].val.clusterDim.y = cluster.y;
         at[n].val.clusterDim.z = cluster.z;
+        ++n;
+        // let the hardware balance the CTAs of a cluster over the SMs (measured a little faster than the default)
+        at[n].id = cudaLaunchAttributeClusterSchedulingPolicyPreference;
+        at[n].val.clusterSchedulingPolicyPreference = cudaClusterSchedulingPolicyLoadBalancing;
         ++n;
     }
     cfg.attrs = n ? at : nullptr;
