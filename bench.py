@@ -328,6 +328,9 @@ def main():
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill"])
     ap.add_argument("--exchange", default="nvlink", choices=["nvlink", "nccl"],
                     help="N > 1: fused combine + NVLink push + ordered sum kernel, or NCCL all-gather + ordered sum")
+    ap.add_argument("--router", action="store_true",
+                    help="decode: produce the routing table on the device inside the timed layer (router matvec + sigmoid "
+                         "top-k kernels ahead of the expert kernels) instead of taking it as an input")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -376,7 +379,21 @@ def main():
     if G > 1:
         final = torch.empty((L, R, H), dtype=torch.float32, device=dev)
 
+    if args.router:
+        # router matrices scaled so that the logits are ~N(0,1) as the workload defines them; the table is then made
+        # on the device, per layer, by the library's router kernels
+        gen = torch.Generator(device=dev).manual_seed(4242)
+        wr_d = (torch.randn((L, E, H), generator=gen, device=dev) / (H ** 0.5)).to(torch.bfloat16)
+        logit_d = torch.empty((L, R, E), dtype=torch.float32, device=dev)
+        p_d = torch.empty_like(p_d)
+        w_d = torch.empty_like(w_d)
+
+    def route(l):
+        if args.router:
+            pkg.route(x_d[l], wr_d[l], logit_d[l], p_d[l], w_d[l])
+
     def layer(l):
+        route(l)
         if G == 1:
             epm.run(l, structs[l], x_d[l], p_d[l], w_d[l], R)
         else:
@@ -440,6 +457,7 @@ def main():
 
     def layers_with_outputs():
         for l in range(L):
+            route(l)
             if G == 1:
                 out_all[l].copy_(epm.run(l, structs[l], x_d[l], p_d[l], w_d[l], R))
             else:
@@ -458,8 +476,9 @@ def main():
 
     def step_e2e():
         x_d.view(torch.int16).copy_(xh, non_blocking=True)
-        p_d.copy_(ph, non_blocking=True)
-        w_d.copy_(wh, non_blocking=True)
+        if not args.router:
+            p_d.copy_(ph, non_blocking=True)
+            w_d.copy_(wh, non_blocking=True)
         if graph_e2e is not None:
             graph_e2e.replay()
         else:
@@ -468,7 +487,7 @@ def main():
         stream.synchronize()
     ms_e2e = timed(step_e2e, max(5, args.steps), 3)
     e2e = {"value": R * L / (ms_e2e / 1e3), "unit": "layer-tokens/s", "ms_per_step": ms_e2e,
-           "h2d_bytes_per_step": L * (R * H * 2 + 2 * R * S * 4), "d2h_bytes_per_step": L * R * H * 4,
+           "h2d_bytes_per_step": L * (R * H * 2 + (0 if args.router else 2 * R * S * 4)), "d2h_bytes_per_step": L * R * H * 4,
            "call": "per step: pinned host inputs of all layers -> device, glmflash_moe_run per layer (graph replay), all layer "
                    "outputs -> pinned host, one synchronize"}
     # the same through the synchronous per-layer host-buffer entry point (glmflash_moe_run_host), N = 1 only
@@ -525,7 +544,8 @@ def main():
                "dtype": "f16xf16->f32", "data": "synthetic", "config": workload_config(args),
                "stack_tokens_per_s": R / (ms_step / 1e3), "graph": graph is not None,
                "clocks": clocks, "e2e": e2e, "exchange": epm.exchange,
-               "gpu_launches": (3 if G == 1 or epm.exchange == "nvlink" else 4) * L * args.steps,
+               "gpu_launches": ((3 if G == 1 or epm.exchange == "nvlink" else 4) + ((1 if R <= 16 else 2) if args.router else 0)) * L * args.steps,
+               "router": "on device, inside the timed layer" if args.router else "routing table is an input",
                "roofline": roofline, "cpu_baseline": cpu}
         print(json.dumps(out))
     finish(world, dist)

@@ -74,6 +74,9 @@ SYMBOLS = {
     "glmflash_ep_connect": (_I, [_P, _P]),
     "glmflash_ep_combine": (_I, [_P, _P, _P, _P, _P, _I, _I]),
     "glmflash_ep_output": (_P, [_P]),
+    "glmflash_router_logits": (_I, [_P, _P, _I, _P, _I, _I, _I, _P, _I]),
+    "glmflash_topk": (_I, [_P, _P, _I, _I, _I, _P, _P, _I]),
+    "glmflash_route": (_I, [_P, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _I]),
     "glmflash_ep_status": (_P, [_P]),
     "glmflash_ep_set_wait_limit": (_I, [_P, C.c_uint32]),
     "glmflash_ep_local_base": (_P, [_P]),
@@ -325,6 +328,30 @@ class Moe(_Owner):
     def output(self):
         import torch
         return _view(lib().glmflash_moe_output(self._h), (self.cfg.max_rows, self.cfg.hidden), torch.float32)
+
+
+def router_logits(x, wr, logits, stream=None, pdl=1):
+    """logits[r][e] = x[r] . wr[e]  (x bf16 [rows][H], wr bf16 [E][H], logits fp32 [rows][E]; CUDA tensors)."""
+    rows, E = logits.shape
+    _check(lib().glmflash_router_logits(_stream_ptr(stream), x.data_ptr(), x.stride(0), wr.data_ptr(), rows, wr.shape[1], E,
+                                        logits.data_ptr(), pdl))
+    return logits
+
+
+def topk(logits, picks, weights, stream=None, pdl=1):
+    """Sigmoid top-k of logits fp32 [rows][E] into picks int32 / weights fp32 [rows][k + 1] (shared expert last)."""
+    rows, E = logits.shape
+    _check(lib().glmflash_topk(_stream_ptr(stream), logits.data_ptr(), rows, E, picks.shape[1] - 1, picks.data_ptr(),
+                               weights.data_ptr(), pdl))
+    return picks, weights
+
+
+def route(x, wr, logits, picks, weights, stream=None, pdl=1):
+    """router_logits + topk; one launch for windows of <= 16 rows."""
+    rows, E = logits.shape
+    _check(lib().glmflash_route(_stream_ptr(stream), x.data_ptr(), x.stride(0), wr.data_ptr(), rows, wr.shape[1], E,
+                                picks.shape[1] - 1, logits.data_ptr(), picks.data_ptr(), weights.data_ptr(), pdl))
+    return picks, weights
 
 
 def rank_sum(gathered, out, stream=None):

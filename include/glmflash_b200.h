@@ -212,6 +212,24 @@ int  glmflash_ep_connect_ptrs(glmflash_ep *h, void *const *peer_bases /* world e
  * applies after its all-gather (src/model.rs:485-496, src/comm.rs:1-2).  gathered: fp32 [world][rows][H]. */
 int glmflash_rank_sum(void *stream, const float *gathered, int world, int rows, int hidden, float *out);
 
+/* ---- router next to the path (upstream call sites src/moe.rs:77-111, src/window_ops.rs:159-199) -------------------
+ * Upstream runs precompiled kernels without published source here, so these two follow the benchmark's definition
+ * of the router and their parity with upstream is not pinned.  Both only enqueue work (graph-capturable);
+ * pdl != 0 chains them with programmatic dependent launch like the expert kernels.
+ * logits[r][e] = sum_k x[r][k] * wr[e][k]: x bf16 [rows][x_stride >= hidden], wr bf16 [experts][hidden], logits fp32
+ * [rows][experts], fp32 accumulation. */
+int glmflash_router_logits(void *stream, const uint16_t *x, int x_stride, const uint16_t *wr, int rows, int hidden,
+                           int experts, float *logits, int pdl);
+/* Sigmoid top-k: per row the topk largest logits (ties to the lower expert id) in descending order,
+ * weight = sigmoid(logit) / sum of the chosen sigmoids; the last slot names the shared expert (id = experts) with
+ * weight 1.  picks int32 [rows][topk + 1], weights fp32 [rows][topk + 1]: the routing table glmflash_moe_run takes. */
+int glmflash_topk(void *stream, const float *logits, int rows, int experts, int topk, int32_t *picks, float *weights,
+                  int pdl);
+/* Both steps: windows of <= 16 rows take ONE launch (a CTA per row computes the row's logits and selects), larger
+ * windows the two kernels above.  logits (fp32 [rows][experts], caller's) receives the logits in both cases. */
+int glmflash_route(void *stream, const uint16_t *x, int x_stride, const uint16_t *wr, int rows, int hidden, int experts,
+                   int topk, float *logits, int32_t *picks, float *weights, int pdl);
+
 #ifdef __cplusplus
 }
 #endif

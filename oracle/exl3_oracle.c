@@ -398,6 +398,53 @@ int gfo_grouping(const int *picks, int rows, int slots, int E1, int maxm, int *i
     return 0;
 }
 
+/* ---------------------------------------------------------------- router (next to the path) */
+
+/* Router logits (call site src/moe.rs:77-95; the reference's kernels here are precompiled without source, so this is
+ * the semantic form: PARITY UNPINNED): logits[r][e] = sum_k x[r][k] * wr[e][k], x and wr bf16 (given as their bit
+ * patterns), accumulated in double and rounded to fp32. */
+void gfo_router_logits(const uint16_t *x, int x_stride, const uint16_t *wr, int rows, int H, int E, float *logits) {
+    for (int r = 0; r < rows; ++r)
+        for (int e = 0; e < E; ++e) {
+            double acc = 0.0;
+            for (int k = 0; k < H; ++k) {
+                uint32_t a = (uint32_t)x[(size_t)r * x_stride + k] << 16, b = (uint32_t)wr[(size_t)e * H + k] << 16;
+                float fa, fb;
+                memcpy(&fa, &a, 4); memcpy(&fb, &b, 4);
+                acc += (double)fa * (double)fb;
+            }
+            logits[(size_t)r * E + e] = (float)acc;
+        }
+}
+
+/* Top-k of the sigmoid router (the benchmark's definition; the reference's _topk has no source: PARITY UNPINNED):
+ * the topk largest logits of a row, ties to the lower expert id, in descending order; weight = sigmoid(logit)
+ * divided by the sum of the chosen sigmoids (fp32); the row's last slot names the shared expert (id E), weight 1.
+ * picks, weights: [rows][topk + 1]. */
+void gfo_topk(const float *logits, int rows, int E, int topk, int *picks, float *weights) {
+    for (int r = 0; r < rows; ++r) {
+        const float *l = logits + (size_t)r * E;
+        int *pk = picks + (size_t)r * (topk + 1);
+        float *w = weights + (size_t)r * (topk + 1);
+        float sum = 0.f;
+        for (int j = 0; j < topk; ++j) {
+            int best = -1;
+            for (int e = 0; e < E; ++e) {
+                int taken = 0;
+                for (int q = 0; q < j; ++q) taken |= pk[q] == e;
+                if (taken) continue;
+                if (best < 0 || l[e] > l[best]) best = e;
+            }
+            pk[j] = best;
+            w[j] = 1.f / (1.f + expf(-l[best]));
+            sum += w[j];
+        }
+        for (int j = 0; j < topk; ++j) w[j] = w[j] / sum;
+        pk[topk] = E;
+        w[topk] = 1.f;
+    }
+}
+
 int gfo_max_threads(void) {
 #ifdef _OPENMP
     return omp_get_max_threads();

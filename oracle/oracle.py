@@ -168,5 +168,23 @@ def grouping(picks, rows, slots, E1, maxm):
     return ids, int(count[0]), members
 
 
+def router_logits(x_bf16_bits, wr_bf16_bits, rows, H, E):
+    """x [rows][H], wr [E][H] as uint16 bf16 bit patterns -> logits fp32 [rows][E] (double accumulation)."""
+    x = _c(x_bf16_bits, np.uint16)
+    wr = _c(wr_bf16_bits, np.uint16)
+    out = np.empty((rows, E), np.float32)
+    lib().gfo_router_logits(_p(x), C.c_int(H), _p(wr), C.c_int(rows), C.c_int(H), C.c_int(E), _p(out))
+    return out
+
+
+def topk(logits, rows, E, k):
+    """-> picks int32 [rows][k+1], weights fp32 [rows][k+1] (shared expert id E, weight 1, in the last slot)."""
+    logits = _c(logits, np.float32)
+    picks = np.empty((rows, k + 1), np.int32)
+    weights = np.empty((rows, k + 1), np.float32)
+    lib().gfo_topk(_p(logits), C.c_int(rows), C.c_int(E), C.c_int(k), _p(picks), _p(weights))
+    return picks, weights
+
+
 def max_threads():
     return lib().gfo_max_threads()

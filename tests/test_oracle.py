@@ -114,3 +114,33 @@ def test_expert_pipeline_modes_agree(oracle, synth):
     out = oracle.combine(y1, rw, 2, S, H)
     want = (rw[:, : S - 1, None] * y1.reshape(2, S, H)[:, : S - 1]).sum(1) + y1.reshape(2, S, H)[:, S - 1]
     assert rel_err(out, want)[0] < 1e-6
+
+
+def test_topk_matches_the_route_generator(oracle):
+    """The oracle's sigmoid top-k against the numpy definition that generates the benchmark's routing tables
+    (glm-flash-rs_b200/synth.py: sigmoid scores, top-4, ties to the lower id, renormalised weights)."""
+    g = np.random.default_rng(99)
+    rows, E, k = 64, 64, 4
+    logits = g.standard_normal((rows, E)).astype(np.float32)
+    logits[5, :] = 1.5                                           # all tied
+    scores = 1.0 / (1.0 + np.exp(-logits.astype(np.float64)))
+    order = np.argsort(-scores, axis=1, kind="stable")[:, :k]
+    top = np.take_along_axis(scores, order, axis=1)
+    want_w = top / top.sum(axis=1, keepdims=True)
+    picks, weights = oracle.topk(logits, rows, E, k)
+    assert np.array_equal(picks[:, :k], order) and (picks[:, k] == E).all()
+    assert np.allclose(weights[:, :k], want_w, rtol=1e-6, atol=1e-7) and (weights[:, k] == 1.0).all()
+
+
+def test_router_logits_small(oracle):
+    g = np.random.default_rng(3)
+    rows, Hs, E = 3, 64, 5
+    xf = g.standard_normal((rows, Hs)).astype(np.float32)
+    wf = g.standard_normal((E, Hs)).astype(np.float32)
+    xb = (xf.view(np.uint32) >> 16).astype(np.uint16)            # truncated to bf16 bit patterns (exact inputs)
+    wb = (wf.view(np.uint32) >> 16).astype(np.uint16)
+    x32 = (xb.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    w32 = (wb.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    want = (x32 @ w32.T).astype(np.float32)
+    got = oracle.router_logits(xb, wb, rows, Hs, E)
+    assert np.allclose(got, want, rtol=1e-6, atol=1e-6)
