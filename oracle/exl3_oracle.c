@@ -13,11 +13,15 @@
  *   pair / member codes native/exl3.cu:160-166,228-231
  *   grouping contract   native/grouping.cu:67-100, src/grouping.rs:143-192
  *   combine             src/moe.rs:171-181 (call site; the kernel's source is absent upstream)
+ *   router, top-k       src/moe.rs:77-111 (call sites; sources absent upstream: the benchmark's definition, PARITY UNPINNED)
  *
  * Pinning: the reference's own known-answer tests for this path are hadamard_involution and
  * codebook_finite (src/experts.rs:566-583); both are reproduced in tests/.  The reference holds no
- * golden vectors for expert outputs.  The GPU tests additionally compare this oracle with the
- * reference's own CUDA kernels compiled unmodified for sm_100a (oracle/_ref).
+ * golden vectors for expert outputs; tests/golden/ref_sm100.npz holds outputs of the reference's own
+ * CUDA kernels (compiled unmodified for sm_100a, run on a B200 by tests/golden/make_golden.py): its
+ * trellis decode, its decode-path and prefill-path layer results and its grouping.  tests/test_golden.py
+ * checks this oracle against them on the CPU (decode and grouping bit-exact), and the GPU tests compare
+ * the oracle with the same kernels live (oracle/_ref).
  *
  * Build: make -C oracle   (gcc -O2 -fopenmp -ffp-contract=off; contraction is off so that the
  * fp32 accumulation is mul-then-add exactly as the reference's scalar Rust).
