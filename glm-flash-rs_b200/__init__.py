@@ -16,7 +16,8 @@ SO_PATH = os.environ.get("GLMFLASH_B200_SO") or os.path.join(_HERE, "libglmflash
 class Config(C.Structure):
     _fields_ = [("hidden", C.c_int32), ("inter", C.c_int32), ("experts", C.c_int32), ("slots", C.c_int32),
                 ("max_rows", C.c_int32), ("shared_exl3", C.c_int32), ("expert_lo", C.c_int32),
-                ("expert_hi", C.c_int32), ("limit", C.c_float), ("pdl", C.c_int32), ("reserved", C.c_int32 * 6)]
+                ("expert_hi", C.c_int32), ("limit", C.c_float), ("pdl", C.c_int32), ("shared_row_lo", C.c_int32),
+                ("shared_row_hi", C.c_int32), ("reserved", C.c_int32 * 4)]
 
 
 class Weights(C.Structure):
@@ -113,9 +114,9 @@ def _check(rc):
 
 
 def make_config(hidden=2048, inter=1536, experts=64, slots=5, max_rows=1, shared_exl3=1, expert_lo=0,
-                expert_hi=None, limit=10.0, pdl=1):
+                expert_hi=None, limit=10.0, pdl=1, shared_rows=(0, 0)):
     return Config(hidden, inter, experts, slots, max_rows, shared_exl3, expert_lo,
-                  experts if expert_hi is None else expert_hi, limit, pdl)
+                  experts if expert_hi is None else expert_hi, limit, pdl, shared_rows[0], shared_rows[1])
 
 
 def _torch():

@@ -9,6 +9,11 @@
 //               (source rank, CTA) carries the epoch;
 //   3. wait:    the same CTA spins (bounded) on its own GPU's flags until every source has delivered the epoch;
 //   4. sum:     the slots are added in ascending rank order -- the reference's determinism rule -- into out.
+// Windows of more than 16 rows use a two-step form of the same kernel (ep_exchange_rows_kernel): every row has
+// one owner rank (chunks of 8 rows, dealt out in contiguous runs); every rank stores its partial of the row only into the
+// OWNER's receive slot, the owner
+// adds the slots in rank order and stores the finished row into every rank's result buffer, and every rank waits for
+// that.  Per rank about 2 x rows x H x 4 bytes cross NVLink instead of world x that (268 MB at 4096 rows on 8 GPUs).
 // Receive buffers are double-buffered by epoch parity; the epoch lives in device memory and is advanced by the
 // last CTA of a call, so captured graphs replay correctly.  A wait that gives up sets the status word (the
 // analogue of upstream's poison word, native/roce.cu:127-141) and the kernel returns; nothing spins unbounded.
@@ -23,11 +28,6 @@ int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limi
 constexpr int EP_MAX_WORLD = 8;
 constexpr int EP_THREADS = 256;
 
-struct EpPeers {
-    float *recv[EP_MAX_WORLD];          // recv[k]: rank k's receive buffer [2][world][max_rows][H] (peer-mapped)
-    unsigned *flags[EP_MAX_WORLD];      // flags[k]: rank k's flags [2][world][max_ctas]
-};
-
 __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned *p) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
@@ -37,12 +37,53 @@ __device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+struct EpPeers {
+    float *recv[EP_MAX_WORLD];          // recv[k]: rank k's receive buffer [2][world][max_rows][H] (peer-mapped)
+    unsigned *flags[EP_MAX_WORLD];      // flags[k]: rank k's flags [2][world][max_ctas]
+    float *fin[EP_MAX_WORLD];           // fin[k]: rank k's finished rows [2][max_rows][H]          (two-step form)
+    unsigned *fin_flags[EP_MAX_WORLD];  // fin_flags[k]: rank k's [2][max_ctas]                     (two-step form)
+};
+
+// This rank's partial of row r, columns d..d+3: its computed pairs of the row, weights applied, ascending slots.
+__device__ __forceinline__ float4 ep_partial(const float *__restrict__ Y, const int *__restrict__ picks,
+                                             const float *__restrict__ route_w, int r, int d, int slots, int H, int E,
+                                             int shared_exl3, int e_lo, int e_hi, int srow_lo, int srow_hi) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < slots; ++s) {
+        const int e = picks[r * slots + s];
+        bool skip = e < 0 || e > E || (e == E ? !shared_exl3 : (e < e_lo || e >= e_hi));
+        if (e == E && srow_hi > srow_lo && (r < srow_lo || r >= srow_hi)) skip = true;      // shared expert: row window
+        if (skip) continue;
+        const float4 y = *reinterpret_cast<const float4 *>(Y + ((size_t)r * slots + s) * H + d);
+        if (s == slots - 1) { acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w; }
+        else {
+            const float w = route_w[r * slots + s];
+            acc.x += w * y.x; acc.y += w * y.y; acc.z += w * y.z; acc.w += w * y.w;
+        }
+    }
+    return acc;
+}
+
+// Bounded wait for *f == epoch.  Gives up at once when another wait of this call has already run out.
+__device__ __forceinline__ bool ep_wait(const unsigned *f, unsigned epoch, unsigned wait_polls, int *status) {
+    for (unsigned i = 0; i < wait_polls; ++i) {
+        if (ld_acquire_sys(f) == epoch) return true;
+        if ((i & 1023u) == 1023u) {
+            if (*reinterpret_cast<volatile int *>(status) == GF_STATUS_PEER_TIMEOUT) break;
+            __nanosleep(200);
+        }
+    }
+    atomicExch(status, GF_STATUS_PEER_TIMEOUT);
+    return false;
+}
+
 __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
                                                                 const float *__restrict__ route_w, float *__restrict__ out,
                                                                 EpPeers peers, unsigned *epoch_ptr, unsigned *done_ptr,
                                                                 int *status, int rank, int world, int rows, int max_rows,
                                                                 int max_ctas, int slots, int H, int E, int shared_exl3,
-                                                                int e_lo, int e_hi, unsigned wait_polls) {
+                                                                int e_lo, int e_hi, int srow_lo, int srow_hi,
+                                                                unsigned wait_polls) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ int ok_sh;
@@ -52,21 +93,9 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
     const unsigned epoch = *epoch_ptr + 1u;                   // every CTA reads it before the last one advances it
     const unsigned par = epoch & 1u;
     const size_t slot_elems = (size_t)max_rows * H;
-    // 1. this rank's partial of row r
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (d < H) {
-        for (int s = 0; s < slots; ++s) {
-            const int e = picks[r * slots + s];
-            const bool skip = e < 0 || e > E || (e == E ? !shared_exl3 : (e < e_lo || e >= e_hi));
-            if (skip) continue;
-            const float4 y = *reinterpret_cast<const float4 *>(Y + ((size_t)r * slots + s) * H + d);
-            if (s == slots - 1) { acc.x += y.x; acc.y += y.y; acc.z += y.z; acc.w += y.w; }
-            else {
-                const float w = route_w[r * slots + s];
-                acc.x += w * y.x; acc.y += w * y.y; acc.z += w * y.z; acc.w += w * y.w;
-            }
-        }
-        // 2. push into slot `rank` of every rank's receive buffer (its own included)
+        // 1. this rank's partial of row r; 2. push into slot `rank` of every rank's receive buffer (its own included)
+        const float4 acc = ep_partial(Y, picks, route_w, r, d, slots, H, E, shared_exl3, e_lo, e_hi, srow_lo, srow_hi);
         for (int k = 0; k < world; ++k) {
             float *dst = peers.recv[k] + ((size_t)par * world + rank) * slot_elems + (size_t)r * H + d;
             *reinterpret_cast<float4 *>(dst) = acc;
@@ -79,15 +108,8 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
     // 3. wait for every source's copy of this CTA's region
     if (threadIdx.x == 0) ok_sh = 1;
     __syncthreads();
-    if (threadIdx.x < world) {
-        const unsigned *f = peers.flags[rank] + ((size_t)par * world + threadIdx.x) * max_ctas + cta;
-        bool got = false;
-        for (unsigned i = 0; i < wait_polls; ++i) {
-            if (ld_acquire_sys(f) == epoch) { got = true; break; }
-            if ((i & 1023u) == 1023u) __nanosleep(200);
-        }
-        if (!got) { ok_sh = 0; atomicExch(status, GF_STATUS_PEER_TIMEOUT); }
-    }
+    if (threadIdx.x < world)
+        if (!ep_wait(peers.flags[rank] + ((size_t)par * world + threadIdx.x) * max_ctas + cta, epoch, wait_polls, status)) ok_sh = 0;
     __syncthreads();
     // 4. ordered sum
     if (d < H && ok_sh) {
@@ -110,6 +132,79 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
         }
     }
 }
+
+// Two-step form for large windows (see the head of this file).  CTA = chunk of EP_RB consecutive rows, all columns; a
+// chunk has one owner rank (the owners' row ranges are multiples of EP_RB), so one fence and one flag per chunk and step
+// replace one per row.  A CTA only ever waits for the CTAs of the SAME chunk on other ranks, and every rank walks the
+// chunks in the same order, so no wait depends on a CTA that is dispatched later on its own GPU.
+constexpr int EP_RB = 8;
+__global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
+                                                                      const float *__restrict__ route_w, float *__restrict__ out,
+                                                                      EpPeers peers, unsigned *epoch_ptr, unsigned *done_ptr,
+                                                                      int *status, int rank, int world, int rows, int max_rows,
+                                                                      int max_ctas, int slots, int H, int E, int shared_exl3,
+                                                                      int e_lo, int e_hi, int srow_lo, int srow_hi,
+                                                                      unsigned wait_polls) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ int ok_sh;
+    const int chunk = blockIdx.x, r0 = chunk * EP_RB, r1 = min(r0 + EP_RB, rows);
+    const unsigned epoch = *epoch_ptr + 1u;
+    const unsigned par = epoch & 1u;
+    const size_t slot_elems = (size_t)max_rows * H;
+    const int chunks = (rows + EP_RB - 1) / EP_RB, per = (chunks + world - 1) / world;
+    const int owner = chunk / per;                            // < world because chunk < chunks
+    const int q4 = H >> 2, items = (r1 - r0) * q4;            // float4 pieces of the chunk
+    // 1. this rank's partial of the chunk goes to the owner's slot `rank`
+    for (int i = threadIdx.x; i < items; i += EP_THREADS) {
+        const int r = r0 + i / q4, d = (i % q4) * 4;
+        const float4 acc = ep_partial(Y, picks, route_w, r, d, slots, H, E, shared_exl3, e_lo, e_hi, srow_lo, srow_hi);
+        *reinterpret_cast<float4 *>(peers.recv[owner] + ((size_t)par * world + rank) * slot_elems + (size_t)r * H + d) = acc;
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) { st_release_sys(peers.flags[owner] + ((size_t)par * world + rank) * max_ctas + chunk, epoch); ok_sh = 1; }
+    __syncthreads();
+    // 2. the owner adds the slots in rank order and stores the finished rows into every rank's result buffer
+    if (owner == rank) {
+        if (threadIdx.x < world)
+            if (!ep_wait(peers.flags[rank] + ((size_t)par * world + threadIdx.x) * max_ctas + chunk, epoch, wait_polls, status)) ok_sh = 0;
+        __syncthreads();
+        if (ok_sh)
+            for (int i = threadIdx.x; i < items; i += EP_THREADS) {
+                const size_t off = (size_t)(r0 + i / q4) * H + (i % q4) * 4;
+                const float *src = peers.recv[rank] + (size_t)par * world * slot_elems + off;
+                float4 sum = __ldcg(reinterpret_cast<const float4 *>(src));
+                for (int k = 1; k < world; ++k) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)k * slot_elems));
+                    sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+                }
+                for (int k = 0; k < world; ++k)
+                    *reinterpret_cast<float4 *>(peers.fin[k] + (size_t)par * slot_elems + off) = sum;
+            }
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x < world && ok_sh) st_release_sys(peers.fin_flags[threadIdx.x] + (size_t)par * max_ctas + chunk, epoch);
+    }
+    // 3. everyone waits for the finished chunk and copies it to the output
+    if (threadIdx.x == 0)
+        if (!ep_wait(peers.fin_flags[rank] + (size_t)par * max_ctas + chunk, epoch, wait_polls, status)) ok_sh = 0;
+    __syncthreads();
+    if (ok_sh)
+        for (int i = threadIdx.x; i < items; i += EP_THREADS) {
+            const size_t off = (size_t)(r0 + i / q4) * H + (i % q4) * 4;
+            *reinterpret_cast<float4 *>(out + off) =
+                __ldcg(reinterpret_cast<const float4 *>(peers.fin[rank] + (size_t)par * slot_elems + off));
+        }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (atomicAdd(done_ptr, 1u) == gridDim.x - 1u) {
+            *done_ptr = 0u;
+            __threadfence();
+            *epoch_ptr = epoch;
+        }
+    }
+}
 }  // namespace gf
 
 using namespace gf;
@@ -118,7 +213,7 @@ struct glmflash_ep {
     glmflash_config cfg;
     int rank = 0, world = 1, max_ctas = 0;
     unsigned char *local = nullptr;               // one allocation: recv | flags | epoch | done | status
-    size_t recv_bytes = 0, flag_bytes = 0, total_bytes = 0;
+    size_t recv_bytes = 0, flag_bytes = 0, fin_bytes = 0, fin_flag_bytes = 0, total_bytes = 0;
     void *peer_base[EP_MAX_WORLD] = {};
     bool opened[EP_MAX_WORLD] = {};
     bool connected = false;
@@ -140,7 +235,9 @@ extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int
     h->max_ctas = (int)(((H / 4 + EP_THREADS - 1) / EP_THREADS) * R);
     h->recv_bytes = (size_t)2 * world * R * H * 4;
     h->flag_bytes = ((size_t)2 * world * h->max_ctas * 4 + 255) / 256 * 256;
-    h->total_bytes = h->recv_bytes + h->flag_bytes + 256;
+    h->fin_bytes = R > 16 ? (size_t)2 * R * H * 4 : 0;        // the two-step form serves windows of more than 16 rows
+    h->fin_flag_bytes = R > 16 ? ((size_t)2 * h->max_ctas * 4 + 255) / 256 * 256 : 0;
+    h->total_bytes = h->recv_bytes + h->flag_bytes + h->fin_bytes + h->fin_flag_bytes + 256;
     if (cudaMalloc((void **)&h->local, h->total_bytes) != cudaSuccess || cudaMemset(h->local, 0, h->total_bytes) != cudaSuccess ||
         cudaMalloc((void **)&h->out, R * H * 4) != cudaSuccess) {
         glmflash_ep_free(h);
@@ -195,12 +292,19 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
     for (int k = 0; k < h->world; ++k) {
         peers.recv[k] = (float *)h->peer_base[k];
         peers.flags[k] = (unsigned *)((unsigned char *)h->peer_base[k] + h->recv_bytes);
+        peers.fin[k] = (float *)((unsigned char *)h->peer_base[k] + h->recv_bytes + h->flag_bytes);
+        peers.fin_flags[k] = (unsigned *)((unsigned char *)h->peer_base[k] + h->recv_bytes + h->flag_bytes + h->fin_bytes);
     }
-    unsigned *epoch = (unsigned *)(h->local + h->recv_bytes + h->flag_bytes);
+    unsigned *epoch = (unsigned *)(h->local + h->recv_bytes + h->flag_bytes + h->fin_bytes + h->fin_flag_bytes);
     const dim3 grid((unsigned)((c.hidden / 4 + EP_THREADS - 1) / EP_THREADS), (unsigned)rows);
+    if (rows > 16 && h->world > 1)
+        return launch_k(ep_exchange_rows_kernel, dim3((unsigned)((rows + EP_RB - 1) / EP_RB)), dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w,
+                        h->out, peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas,
+                        c.slots, c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi,
+                        h->wait_polls);
     return launch_k(ep_combine_kernel, grid, dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w, h->out,
                     peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas, c.slots,
-                    c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, h->wait_polls);
+                    c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi, h->wait_polls);
 }
 
 extern "C" int glmflash_ep_set_wait_limit(glmflash_ep *h, uint32_t polls) {
@@ -226,5 +330,5 @@ extern "C" int glmflash_ep_connect_ptrs(glmflash_ep *h, void *const *peer_bases)
 
 extern "C" float *glmflash_ep_output(const glmflash_ep *h) { return h ? h->out : nullptr; }
 extern "C" const int32_t *glmflash_ep_status(const glmflash_ep *h) {
-    return h ? (const int32_t *)(h->local + h->recv_bytes + h->flag_bytes + 8) : nullptr;
+    return h ? (const int32_t *)(h->local + h->recv_bytes + h->flag_bytes + h->fin_bytes + h->fin_flag_bytes + 8) : nullptr;
 }

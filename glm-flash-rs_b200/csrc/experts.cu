@@ -58,6 +58,8 @@ int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limi
     GF_REQUIRE(cfg->expert_lo >= 0 && cfg->expert_hi <= cfg->experts && cfg->expert_lo <= cfg->expert_hi,
                "expert window must satisfy 0 <= lo <= hi <= experts");
     GF_REQUIRE(cfg->limit > 0.f, "limit must be positive");
+    GF_REQUIRE(cfg->shared_row_lo >= 0 && cfg->shared_row_lo <= cfg->shared_row_hi, "shared-expert row window must satisfy 0 <= lo <= hi");
+    GF_REQUIRE(cfg->shared_row_hi == 0 || cfg->max_rows > 16, "a shared-expert row window needs a handle for more than 16 rows");
     int dev_count = 0;
     if (cudaGetDeviceCount(&dev_count) != cudaSuccess || dev_count == 0) return fail("no CUDA device: there is no CPU path");
     return 0;

@@ -65,13 +65,14 @@ constexpr int PLAN_PAIR_BASE = 4, PLAN_SINGLE_BASE = PLAN_PAIR_BASE + FG_MAXU + 
 // block b writes the grouped rows of distinct expert b.
 __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restrict__ ids, const int *__restrict__ count,
                                                           const int *__restrict__ members, int maxm, int slots, int E,
-                                                          int shared_exl3, int e_lo, int e_hi, int *__restrict__ plan,
-                                                          int *__restrict__ src_pair, int *__restrict__ row_expert) {
-    __shared__ int cnt_sh[FG_MAXU], row_sh[FG_MAXU], e_sh[FG_MAXU];
+                                                          int shared_exl3, int e_lo, int e_hi, int srow_lo, int srow_hi,
+                                                          int *__restrict__ plan, int *__restrict__ src_pair,
+                                                          int *__restrict__ row_expert) {
+    __shared__ int cnt_sh[FG_MAXU], row_sh[FG_MAXU], e_sh[FG_MAXU], first_sh[FG_MAXU];
     __shared__ int wsum[4][32];
     const int u = threadIdx.x, lane = u & 31, warp = u >> 5;
     const int n = min(count[0], FG_MAXU);
-    int cnt = 0, e = -1;
+    int cnt = 0, e = -1, first = 0;
     if (u < n) {
         e = ids[u];
         if (!expert_skipped(e, E, shared_exl3, e_lo, e_hi)) {
@@ -82,6 +83,20 @@ __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restric
                 if (m[mid] >= 0) lo = mid + 1; else hi = mid;
             }
             cnt = lo;
+            if (e == E && srow_hi > srow_lo) {
+                // the shared expert is computed here for a window of rows only: members ascend by row (code = row * 32
+                // + slot), so the window is a contiguous run of the list
+                auto lower = [&](int row) {                 // first member whose row is >= `row`
+                    int a = 0, b = cnt;
+                    while (a < b) {
+                        const int mid = (a + b) >> 1;
+                        if ((m[mid] >> 5) < row) a = mid + 1; else b = mid;
+                    }
+                    return a;
+                };
+                first = lower(srow_lo);
+                cnt = lower(srow_hi) - first;
+            }
         }
     }
     const int tiles = (cnt + FG_BM - 1) / FG_BM;
@@ -102,7 +117,7 @@ __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restric
         p_all += wsum[0][w]; s_all += wsum[1][w]; r_all += wsum[2][w]; t_all += wsum[3][w];
     }
     const int p_ex = p_off + p_inc - pairs, s_ex = s_off + s_inc - single, r_ex = r_off + r_inc - cnt;
-    cnt_sh[u] = cnt; row_sh[u] = r_ex; e_sh[u] = e;
+    cnt_sh[u] = cnt; row_sh[u] = r_ex; e_sh[u] = e; first_sh[u] = first;
     if (blockIdx.x == 0) {
         plan[PLAN_PAIR_BASE + u] = p_ex;
         plan[PLAN_SINGLE_BASE + u] = s_ex;
@@ -116,9 +131,9 @@ __global__ void __launch_bounds__(FG_MAXU) fast_plan_kernel(const int *__restric
     }
     __syncthreads();
     for (int uu = blockIdx.x; uu < n; uu += gridDim.x) {
-        const int c = cnt_sh[uu], rb = row_sh[uu], ee = e_sh[uu];
+        const int c = cnt_sh[uu], rb = row_sh[uu], ee = e_sh[uu], f0 = first_sh[uu];
         for (int m = u; m < c; m += FG_MAXU) {
-            const int code = members[(size_t)uu * maxm + m];
+            const int code = members[(size_t)uu * maxm + f0 + m];
             src_pair[rb + m] = (code >> 5) * slots + (code & 31);
             row_expert[rb + m] = ee;
         }
@@ -697,7 +712,7 @@ extern "C" int glmflash_fast_experts_run(glmflash_fast_experts *f, void *stream,
     const long P = (long)rows * c.slots;
     if (f->phases & 1)
         fast_plan_kernel<<<c.experts + 1, FG_MAXU, 0, s>>>(ids, count, members, maxm, c.slots, c.experts, c.shared_exl3, c.expert_lo,
-                                              c.expert_hi, f->plan, f->src_pair, f->row_expert);
+                                              c.expert_hi, c.shared_row_lo, c.shared_row_hi, f->plan, f->src_pair, f->row_expert);
     GF_CUDA(cudaGetLastError());
     const int mats = shared_x ? 1 : 2;
     if (f->phases & 2)

@@ -18,7 +18,8 @@ int experts_run_fused(glmflash_experts *e, cudaStream_t s, const glmflash_weight
 // fp32, ascending slot order, shared last: the order of the oracle's combine.
 __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
                                                       const float *__restrict__ route_w, float *__restrict__ out, int rows,
-                                                      int slots, int H, int E, int shared_exl3, int e_lo, int e_hi) {
+                                                      int slots, int H, int E, int shared_exl3, int e_lo, int e_hi,
+                                                      int srow_lo, int srow_hi) {
     // The routing table and the weights were complete before the expert kernels ran (those read them), so they are
     // fetched ahead of the dependency wait; only the pair results Y belong to the kernel in front.
     const int r = blockIdx.y;
@@ -32,6 +33,7 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
         if (s < slots) {
             const int e = picks[r * slots + s];
             keep = !(e < 0 || e > E || (e == E ? !shared_exl3 : (e < e_lo || e >= e_hi)));
+            if (e == E && srow_hi > srow_lo && (r < srow_lo || r >= srow_hi)) keep = false;   // shared expert: row window
             w = route_w[r * slots + s];
         }
         wgt_sh[s] = w;
@@ -72,7 +74,7 @@ int launch_combine(cudaStream_t s, const float *Y, const int *picks, const float
                    const glmflash_config &c) {
     const dim3 grid((unsigned)((c.hidden / 4 + 255) / 256), (unsigned)rows);
     return launch_k(combine_kernel, grid, dim3(256), 0, s, c.pdl != 0, Y, picks, route_w, out, rows, c.slots, c.hidden,
-                    c.experts, c.shared_exl3, c.expert_lo, c.expert_hi);
+                    c.experts, c.shared_exl3, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi);
 }
 }  // namespace gf
 

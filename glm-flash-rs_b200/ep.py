@@ -4,7 +4,8 @@ The reference shards every expert four ways by tensor parallelism and, after eac
 ranks' fp32 partial outputs and adds them in fixed rank order (src/model.rs:485-496, src/comm.rs:1-2: "never sum
 in NCCL").  Here the shards are whole experts:
   * routed expert e lives on rank e // (experts / world)              (contiguous windows)
-  * the shared expert (every row uses it) is owned by rank  layer % world   (round robin over the layers)
+  * the shared expert (every row uses it): windows of <= 16 rows -- owned by rank  layer % world  (round robin over
+    the layers); larger windows (prefill) -- split by ROWS, rank k computes it for rows [k, k+1) * ceil(max_rows / world)
   * grouping runs on every rank from the replicated picks (deterministic, so the ranks agree without talking)
   * each rank computes the pairs of its window and combines them into a partial out_g[rows][hidden] fp32
   * exchange = all-gather of the partials over NVLink (NCCL) + the same fixed rank-order sum as the reference
@@ -27,13 +28,25 @@ def shared_owner(layer, world):
     return layer % world
 
 
-def computed_here(picks, rank, world, experts, layer):
-    """Boolean mask [rows][slots]: which pairs this rank computes (the library's window rule)."""
+def shared_rows(rank, world, max_rows):
+    """[lo, hi) of window rows whose shared-expert pair `rank` computes in a handle for more than 16 rows."""
+    per = -(-max_rows // world)
+    return rank * per, (rank + 1) * per
+
+
+def computed_here(picks, rank, world, experts, layer, max_rows=None):
+    """Boolean mask [rows][slots]: which pairs this rank computes (the library's window rule).  max_rows: the handle's
+    row capacity; above 16 the shared expert is split by rows instead of going to one rank per layer."""
     import numpy as np
     lo, hi = expert_window(rank, world, experts)
     picks = np.asarray(picks)
     routed = (picks >= lo) & (picks < hi) & (picks < experts)
-    shared = (picks >= experts) & (shared_owner(layer, world) == rank)
+    if max_rows is not None and max_rows > 16 and world > 1:
+        rlo, rhi = shared_rows(rank, world, max_rows)
+        rows = np.arange(picks.shape[0])[:, None]
+        shared = (picks == experts) & (rows >= rlo) & (rows < rhi)
+    else:
+        shared = (picks == experts) & (shared_owner(layer, world) == rank)
     return routed | shared
 
 
@@ -66,9 +79,11 @@ class EpMoe:
         self.pkg, self.rank, self.world, self.group = pkg, rank, world, group
         self.experts, self.hidden, self.exchange = experts, hidden, exchange if world > 1 else "none"
         lo, hi = expert_window(rank, world, experts)
-        kinds = (1,) if world == 1 else (0, 1)
+        self.row_split = world > 1 and max_rows > 16           # prefill: the shared expert is split by rows
+        srows = shared_rows(rank, world, max_rows) if self.row_split else (0, 0)
+        kinds = (1,) if world == 1 or self.row_split else (0, 1)
         self.moes = {sh: pkg.Moe(pkg.make_config(hidden, inter, experts, slots, max_rows=max_rows, shared_exl3=sh,
-                                                 expert_lo=lo, expert_hi=hi)) for sh in kinds}
+                                                 expert_lo=lo, expert_hi=hi, shared_rows=srows)) for sh in kinds}
         if self.exchange == "nccl":
             self.gathered = torch.empty((world, max_rows, hidden), dtype=torch.float32, device=device)
             self.final = torch.empty((max_rows, hidden), dtype=torch.float32, device=device)
@@ -77,13 +92,14 @@ class EpMoe:
                 out = [None] * world
                 dist.all_gather_object(out, local, group=group)
                 return out
-            cfg = pkg.make_config(hidden, inter, experts, slots, max_rows=max_rows, shared_exl3=0, expert_lo=lo, expert_hi=hi)
+            cfg = pkg.make_config(hidden, inter, experts, slots, max_rows=max_rows, shared_exl3=0, expert_lo=lo, expert_hi=hi,
+                                  shared_rows=srows)
             self.ep = pkg.EpCombine(cfg, rank, world, gather)
             for m in self.moes.values():
                 m.set_phases(15)                    # experts only: the combine is the fused exchange kernel's first step
 
     def owns_shared(self, layer):
-        return self.world == 1 or shared_owner(layer, self.world) == self.rank
+        return self.world == 1 or self.row_split or shared_owner(layer, self.world) == self.rank
 
     def owner(self, layer):
         return self.moes[1 if self.owns_shared(layer) else 0]

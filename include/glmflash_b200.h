@@ -59,7 +59,10 @@ typedef struct glmflash_config {
     int32_t pdl;           /* 1: chain the kernels of a run with programmatic dependent launch, so that each
                               kernel's weight prefetch overlaps its predecessor's tail (upstream's "pdl" load
                               policy, src/experts.rs:350-354, native/expert_loads.cu:38-44); 0: plain launches */
-    int32_t reserved[6];
+    int32_t shared_row_lo; /* expert-parallel prefill: with shared_exl3 = 1 the shared expert is computed here only   */
+    int32_t shared_row_hi; /* for window rows in [shared_row_lo, shared_row_hi) (0, 0 = every row); handles for more
+                              than 16 rows only                                                              */
+    int32_t reserved[4];
 } glmflash_config;
 
 /* The nine tensors `m.pointer(..moe.experts.*)` resolves upstream (src/experts.rs:467). */

@@ -31,13 +31,15 @@ def _worker(rank, world, port, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         worst = 0.0
-        for layer in range(LAYERS):
+        # (rows, handle capacity): a verify window (shared expert owned by one rank per layer) and a prefill-sized
+        # handle (capacity above 16 rows: the shared expert is split by rows)
+        for layer, (R, cap) in enumerate([(5, None), (5, None), (5, None), (21, 21), (18, 40)]):
             bank = synth.expert_bank(50 + layer, H, I, E, svh_scale=True)
             x = synth.activations_bf16(60 + layer, R, H)
             picks, rw = synth.route(70 + layer, R, E, S - 1)
             Y = O.experts_run_rows(bank, H, I, E + 1, S, x, picks, mode=1, threads=1)
             full = O.combine(Y, rw, R, S, H)
-            mine = ep.computed_here(picks, rank, world, E, layer)
+            mine = ep.computed_here(picks, rank, world, E, layer, max_rows=cap)
             wmask = np.where(mine, np.concatenate([rw[:, :-1], np.ones((R, 1), np.float32)], 1), 0).astype(np.float32)
             # partial combine of this rank: masked pairs contribute nothing (their Y rows are never computed on a GPU rank)
             Ym = np.where(np.repeat(mine.reshape(-1, 1), H, 1), Y, 0).astype(np.float32)

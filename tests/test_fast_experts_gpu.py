@@ -163,3 +163,37 @@ def test_prefill_config4_vs_upstream(pkg, oracle, synth, cuda, bank, dbank):
     out = moe.output[:rows].cpu().numpy()
     want_out = oracle.combine(y, rw, rows, S, H)
     assert rel_err(out, want_out)[0] < 1e-5
+
+
+def test_shared_expert_row_window(pkg, synth, cuda, dbank):
+    """Expert-parallel prefill splits the shared expert by rows: a handle with shared_rows = (lo, hi) computes the shared
+    pair only for window rows in [lo, hi); every other pair is untouched.  Checked against the layer without a row
+    window: out_window[r] = out_full[r] - Y_shared[r] outside the window (same fp32 order: the shared pair is the last
+    term of the sum), identical inside."""
+    import torch
+    rows, lo, hi = 300, 100, 171
+    x = _bf16_dev(synth.activations_bf16(41, rows, H), cuda)
+    picks, rw = synth.route(42, rows, E, S - 1, uniform=True)
+    pd, wd = torch.from_numpy(picks).to(cuda), torch.from_numpy(rw).to(cuda)
+    full = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows))
+    full.run(dbank, x, pd, wd, rows)
+    torch.cuda.synchronize()
+    pairs = pkg._view(full.pairs_ptr.value, (rows, S, H), torch.float32).clone()
+    out_full = full.output[:rows].clone()
+    win = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows, shared_rows=(lo, hi)))
+    for _ in range(2):
+        win.run(dbank, x, pd, wd, rows)
+    torch.cuda.synchronize()
+    got = win.output[:rows]
+    inside = torch.zeros(rows, dtype=torch.bool, device=cuda)
+    inside[lo:hi] = True
+    assert torch.equal(got[inside], out_full[inside])
+    routed_only = out_full - pairs[:, S - 1, :]                 # not bit-exact: (a + s) - s; compare with a tolerance
+    assert torch.allclose(got[~inside], routed_only[~inside], rtol=1e-5, atol=1e-5 * float(out_full.abs().max()))
+    # exact form: routed-only sum in the combine's order
+    want = torch.zeros((rows, H), dtype=torch.float32, device=cuda)
+    for s in range(S - 1):
+        want = torch.addcmul(want, wd[:, s, None], pairs[:, s, :])
+    assert torch.allclose(got[~inside], want[~inside], rtol=2e-6, atol=1e-6 * float(out_full.abs().max()))
+    with pytest.raises(pkg.GlmFlashError):
+        pkg.Moe(pkg.make_config(H, I, E, S, max_rows=16, shared_rows=(0, 8)))   # only handles for more than 16 rows
