@@ -152,21 +152,38 @@ __global__ void __launch_bounds__(256) fast_rot_kernel(const __nv_bfloat16 *__re
     const int KB = K >> 7, rows = plan[1];
     for (int j = blockIdx.x; j < rows; j += gridDim.x) {
         const int p = src_pair[j], e = row_expert[j], row = p / slots;
-        for (int blk = warp; blk < KB; blk += 8) {
-            const int k = blk * 128 + 4 * lane;
-            const uint2 xv = *reinterpret_cast<const uint2 *>(x + (size_t)row * x_stride + k);
-            const __nv_bfloat162 x01 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.x),
-                                 x23 = *reinterpret_cast<const __nv_bfloat162 *>(&xv.y);
-            const float xf[4] = {__bfloat162float(x01.x), __bfloat162float(x01.y), __bfloat162float(x23.x), __bfloat162float(x23.y)};
-            for (int mat = 0; mat < mats; ++mat) {
-                const uint2 sv = *reinterpret_cast<const uint2 *>((mat ? suh1 : suh0) + (size_t)e * K + k);
-                const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv.x), s23 = *reinterpret_cast<const __half2 *>(&sv.y);
-                float v[4] = {xf[0] * __low2float(s01), xf[1] * __high2float(s01), xf[2] * __low2float(s23), xf[3] * __high2float(s23)};
-                fwht128(v, lane);
-                __half2 h01 = __halves2half2(__float2half_rn(v[0] * HAD_SCALE), __float2half_rn(v[1] * HAD_SCALE));
-                __half2 h23 = __halves2half2(__float2half_rn(v[2] * HAD_SCALE), __float2half_rn(v[3] * HAD_SCALE));
-                *reinterpret_cast<uint2 *>((mat ? out1 : out0) + (size_t)j * K + k) =
-                    make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+        // two 128-blocks of the warp per round: all their loads are issued before the first transform
+        for (int blk0 = warp; blk0 < KB; blk0 += 16) {
+            const int n2 = blk0 + 8 < KB ? 2 : 1;
+            uint2 xv[2], sv[2][2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (i >= n2) break;
+                const int k = (blk0 + 8 * i) * 128 + 4 * lane;
+                xv[i] = *reinterpret_cast<const uint2 *>(x + (size_t)row * x_stride + k);
+#pragma unroll
+                for (int mat = 0; mat < 2; ++mat)
+                    if (mat < mats) sv[i][mat] = __ldg(reinterpret_cast<const uint2 *>((mat ? suh1 : suh0) + (size_t)e * K + k));
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                if (i >= n2) break;
+                const int k = (blk0 + 8 * i) * 128 + 4 * lane;
+                const __nv_bfloat162 x01 = *reinterpret_cast<const __nv_bfloat162 *>(&xv[i].x),
+                                     x23 = *reinterpret_cast<const __nv_bfloat162 *>(&xv[i].y);
+                const float xf[4] = {__bfloat162float(x01.x), __bfloat162float(x01.y), __bfloat162float(x23.x), __bfloat162float(x23.y)};
+#pragma unroll
+                for (int mat = 0; mat < 2; ++mat) {
+                    if (mat >= mats) break;
+                    const __half2 s01 = *reinterpret_cast<const __half2 *>(&sv[i][mat].x),
+                                  s23 = *reinterpret_cast<const __half2 *>(&sv[i][mat].y);
+                    float v[4] = {xf[0] * __low2float(s01), xf[1] * __high2float(s01), xf[2] * __low2float(s23), xf[3] * __high2float(s23)};
+                    fwht128(v, lane);
+                    __half2 h01 = __halves2half2(__float2half_rn(v[0] * HAD_SCALE), __float2half_rn(v[1] * HAD_SCALE));
+                    __half2 h23 = __halves2half2(__float2half_rn(v[2] * HAD_SCALE), __float2half_rn(v[3] * HAD_SCALE));
+                    *reinterpret_cast<uint2 *>((mat ? out1 : out0) + (size_t)j * K + k) =
+                        make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+                }
             }
         }
     }
