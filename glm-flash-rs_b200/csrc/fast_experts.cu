@@ -331,8 +331,9 @@ struct FgCfg {
     static constexpr int STAGES = MATS == 2 ? 3 : 4;
     static constexpr int STAGE_BYTES = 3 * FG_TILE_BYTES;                                    // A tile 0, A tile 1, B
     static constexpr int GBUF_BYTES = MATS == 2 ? 64 * 256 * 4 : 0;                          // silu(gate) as bf16 pairs
-    static constexpr int TABLE_BYTES = 256 + 3 * 128 * 4 + 2 * (FG_MAXU + 1) * 4 + 64;
-    static constexpr size_t SMEM = 1024 /*align*/ + (size_t)STAGES * STAGE_BYTES + GBUF_BYTES + TABLE_BYTES;
+    static constexpr int TABLE_BYTES = (256 + 3 * 128 * 4 + 2 * (FG_MAXU + 1) * 4 + 64 + 127) / 128 * 128;   // keeps tbuf 128-byte aligned
+    static constexpr int TBUF_BYTES = MATS == 1 ? 8 * 32 * 16 * 4 : 0;        // down: per epilogue warp 32 rows x 16 floats
+    static constexpr size_t SMEM = 1024 /*align*/ + (size_t)STAGES * STAGE_BYTES + GBUF_BYTES + TABLE_BYTES + TBUF_BYTES;
 };
 
 template <int MATS>
@@ -353,6 +354,7 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     float *scales = reinterpret_cast<float *>(tables + 256);               // [3][128]
     int *pair_base = reinterpret_cast<int *>(tables + 256 + 3 * 128 * 4);  // [FG_MAXU + 1]
     int *single_base = pair_base + FG_MAXU + 1;                            // [FG_MAXU + 1]
+    float *tbuf = reinterpret_cast<float *>(tables + C::TABLE_BYTES);      // [8 warps][32 rows][16] (down only)
     const int *row_base = a.plan + PLAN_ROW_BASE;                          // global (L1 / L2 hits)
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -514,13 +516,31 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                         }
                     }
                 } else {
-                    if (m < cnt) {
-                        const int p = a.src_pair[t.row0 + em];
-                        float4 *o = reinterpret_cast<float4 *>(a.y + (size_t)p * a.N + t.nb * 128);
+                    // down: y rows are pair rows, scattered by src_pair.  A thread owns one row, so direct stores would
+                    // put 32 rows x 16 bytes into every store instruction (half-filled sectors).  The rows go through a
+                    // per-warp shared-memory tile, 16 columns at a time, and leave as 8 rows x 64 contiguous bytes per
+                    // instruction.  Chunk c of row r sits at chunk c ^ ((r >> 1) & 3): conflict-free both ways.
+                    const int p = m < cnt ? a.src_pair[t.row0 + em] : -1;
+                    float *wbuf = tbuf + (warp - 4) * 512;
 #pragma unroll
-                        for (int c = 0; c < 32; ++c)
-                            o[c] = make_float4(v[4 * c] * HAD_SCALE * scales[4 * c], v[4 * c + 1] * HAD_SCALE * scales[4 * c + 1],
-                                               v[4 * c + 2] * HAD_SCALE * scales[4 * c + 2], v[4 * c + 3] * HAD_SCALE * scales[4 * c + 3]);
+                    for (int ch = 0; ch < 8; ++ch) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            const int col = ch * 16 + 4 * c;
+                            *reinterpret_cast<float4 *>(wbuf + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) =
+                                make_float4(v[col] * HAD_SCALE * scales[col], v[col + 1] * HAD_SCALE * scales[col + 1],
+                                            v[col + 2] * HAD_SCALE * scales[col + 2], v[col + 3] * HAD_SCALE * scales[col + 3]);
+                        }
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = (lane >> 2) + 8 * i, c = lane & 3;
+                            const float4 val = *reinterpret_cast<const float4 *>(wbuf + rr * 16 + ((c ^ ((rr >> 1) & 3)) << 2));
+                            const int pr = __shfl_sync(0xffffffffu, p, rr);              // pair row of warp row rr
+                            if (pr >= 0)
+                                *reinterpret_cast<float4 *>(a.y + (size_t)pr * a.N + t.nb * 128 + ch * 16 + 4 * c) = val;
+                        }
+                        __syncwarp();
                     }
                 }
             }
