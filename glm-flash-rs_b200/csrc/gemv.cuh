@@ -66,6 +66,16 @@ constexpr int GEMV_PST = 132;                      // floats per partial row
 
 enum GemvMode : int { GEMV_GATEUP = 0, GEMV_DOWN = 1, GEMV_LINEAR = 2 };
 
+// Barrier of one warp pair (64 threads); ids 1..4, compile-time so that only five barriers are reserved per CTA.
+__device__ __forceinline__ void pair_barrier(int pw) {
+    switch (pw) {
+        case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+        case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+        case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+        default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+    }
+}
+
 struct GemvArgs {
     const __half *X0, *X1;        // rotated inputs [P][K] fp16 (X1: second matrix, MATS = 2)
     const uint32_t *T0, *T1;      // trellis banks [E1][K/16][N/16][32]
@@ -432,51 +442,67 @@ __device__ __forceinline__ int gemv_item(const GemvArgs &a, unsigned char *smem,
     cluster_sync();
     GF_STAMP(8);
 
-    // ---- member m is finished by CTA m % SK: the splits' partials are read from the peers' shared memory and added
-    //      in split order, then the epilogue runs in the warp.
-    for (int m = split + a.SK * warp; m < nmem; m += a.SK * (GEMV_THREADS / 32)) {
-        const int p = rows_sh[m];
-        const int n0 = nb * 128 + 4 * lane;
-        float v0[4] = {0.f, 0.f, 0.f, 0.f}, v1[4] = {0.f, 0.f, 0.f, 0.f};
-        // the splits' partials, four splits per round trip through the cluster's shared memory (all reads of a batch are
-        // issued before its first add); the adds keep the ascending split order
+    // ---- member m is finished by CTA m % SK: the splits' partials are read from the peers' shared memory (all reads
+    //      of a matrix in one batch, one round trip) and added in ascending split order, then the epilogue runs.
+    auto reduce_splits = [&](int plane_row, float (&v)[4]) {
+        float4 q[GEMV_MAX_SPLITS];
 #pragma unroll
-        for (int s0 = 0; s0 < GEMV_MAX_SPLITS; s0 += 4) {
-            if (s0 >= a.SK) break;
-            float4 q[4], r[4];
+        for (int s = 0; s < GEMV_MAX_SPLITS; ++s)
+            if (s < a.SK) q[s] = *reinterpret_cast<const float4 *>(cluster_map(part, s) + (size_t)plane_row * GEMV_PST + 4 * lane);
 #pragma unroll
-            for (int s = 0; s < 4; ++s)
-                if (s0 + s < a.SK) {
-                    const float *rp = cluster_map(part, s0 + s) + (size_t)m * GEMV_PST + 4 * lane;
-                    q[s] = *reinterpret_cast<const float4 *>(rp);
-                    if (MATS == 2) r[s] = *reinterpret_cast<const float4 *>(rp + (size_t)SETS * 8 * GEMV_PST);
+        for (int s = 0; s < GEMV_MAX_SPLITS; ++s)
+            if (s < a.SK) { v[0] += q[s].x; v[1] += q[s].y; v[2] += q[s].z; v[3] += q[s].w; }
+    };
+    if (MATS == 2) {
+        // Two warps per member, side by side: the odd warp sums and transforms the up matrix and hands the clamped
+        // values over through shared memory, the even warp does the same for gate, applies SwiGLU, rotates for the down
+        // projection and stores.  The single-member case (one token) is a serial tail of the whole kernel: this halves it.
+        __shared__ __align__(16) float up_sh[GEMV_THREADS / 64][128];
+        const int pw = warp >> 1, role = warp & 1;
+        for (int m = split + a.SK * pw; m < nmem; m += a.SK * (GEMV_THREADS / 64)) {
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            reduce_splits(role * SETS * 8 + m, v);
+            if (role == 0) GF_STAMP(11);
+            fwht128(v, lane);
+            if (role == 1) {
+                float4 uu;
+                uu.x = fminf(fmaxf(bf16r(v[0] * HAD_SCALE * scale_sh[1][4 * lane]), -a.limit), a.limit);
+                uu.y = fminf(fmaxf(bf16r(v[1] * HAD_SCALE * scale_sh[1][4 * lane + 1]), -a.limit), a.limit);
+                uu.z = fminf(fmaxf(bf16r(v[2] * HAD_SCALE * scale_sh[1][4 * lane + 2]), -a.limit), a.limit);
+                uu.w = fminf(fmaxf(bf16r(v[3] * HAD_SCALE * scale_sh[1][4 * lane + 3]), -a.limit), a.limit);
+                *reinterpret_cast<float4 *>(&up_sh[pw][4 * lane]) = uu;
+                pair_barrier(pw);                                                // up values are there
+            } else {
+                float sg[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float gg = fminf(bf16r(v[j] * HAD_SCALE * scale_sh[0][4 * lane + j]), a.limit);
+                    sg[j] = bf16r(gg / (1.f + expf(-gg)));
                 }
-#pragma unroll
-            for (int s = 0; s < 4; ++s)
-                if (s0 + s < a.SK) {
-                    v0[0] += q[s].x; v0[1] += q[s].y; v0[2] += q[s].z; v0[3] += q[s].w;
-                    if (MATS == 2) { v1[0] += r[s].x; v1[1] += r[s].y; v1[2] += r[s].z; v1[3] += r[s].w; }
-                }
-        }
-        GF_STAMP(11);
-        fwht128(v0, lane);
-        if (MATS == 2) {
-            fwht128(v1, lane);
-            float o[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float gg = fminf(bf16r(v0[j] * HAD_SCALE * scale_sh[0][4 * lane + j]), a.limit);
-                const float uu = fminf(fmaxf(bf16r(v1[j] * HAD_SCALE * scale_sh[1][4 * lane + j]), -a.limit), a.limit);
-                const float act = bf16r(bf16r(gg / (1.f + expf(-gg))) * uu);
-                o[j] = act * scale_sh[2][4 * lane + j];
+                pair_barrier(pw);
+                const float4 uu = *reinterpret_cast<const float4 *>(&up_sh[pw][4 * lane]);
+                float o[4];
+                o[0] = bf16r(sg[0] * uu.x) * scale_sh[2][4 * lane];
+                o[1] = bf16r(sg[1] * uu.y) * scale_sh[2][4 * lane + 1];
+                o[2] = bf16r(sg[2] * uu.z) * scale_sh[2][4 * lane + 2];
+                o[3] = bf16r(sg[3] * uu.w) * scale_sh[2][4 * lane + 3];
+                GF_STAMP(12);
+                fwht128(o, lane);
+                __half2 h01 = __halves2half2(__float2half_rn(o[0] * HAD_SCALE), __float2half_rn(o[1] * HAD_SCALE));
+                __half2 h23 = __halves2half2(__float2half_rn(o[2] * HAD_SCALE), __float2half_rn(o[3] * HAD_SCALE));
+                uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
+                *reinterpret_cast<uint2 *>(a.xd + (size_t)rows_sh[m] * a.N + nb * 128 + 4 * lane) = pk;
             }
-            GF_STAMP(12);
-            fwht128(o, lane);
-            __half2 h01 = __halves2half2(__float2half_rn(o[0] * HAD_SCALE), __float2half_rn(o[1] * HAD_SCALE));
-            __half2 h23 = __halves2half2(__float2half_rn(o[2] * HAD_SCALE), __float2half_rn(o[3] * HAD_SCALE));
-            uint2 pk = make_uint2(*reinterpret_cast<uint32_t *>(&h01), *reinterpret_cast<uint32_t *>(&h23));
-            *reinterpret_cast<uint2 *>(a.xd + (size_t)p * a.N + n0) = pk;
-        } else {
+            pair_barrier(pw);                                                    // up_sh may be written again
+        }
+    } else {
+        for (int m = split + a.SK * warp; m < nmem; m += a.SK * (GEMV_THREADS / 32)) {
+            const int p = rows_sh[m];
+            const int n0 = nb * 128 + 4 * lane;
+            float v0[4] = {0.f, 0.f, 0.f, 0.f};
+            reduce_splits(m, v0);
+            GF_STAMP(11);
+            fwht128(v0, lane);
             float4 o;
             o.x = v0[0] * HAD_SCALE * scale_sh[0][4 * lane];
             o.y = v0[1] * HAD_SCALE * scale_sh[0][4 * lane + 1];
