@@ -12,14 +12,14 @@
 //   rot       the input rotation writes Xs[j] = fp16(H(x[row] * suh[e]) / sqrt 128) in grouped order, so the A
 //             operand of every M tile is a contiguous 128 x K slab that one TMA tensor load brings into shared
 //             memory in the 128-byte-swizzled K-major layout the tensor core reads.
-//   gemm      persistent CTAs, one per SM, 20 warps:
+//   gemm      persistent CTAs, one per SM, 28 warps:
 //               warp 0       TMA producer of the A stages (two M tiles of 128 rows x 64 k)
 //               warp 1       issues tcgen05.mma (M 128 x N 128 x K 16, fp16 -> fp32), commits stages and passes
 //               warp 2       allocates / frees tensor memory (512 columns)
 //               warps 4-11   epilogue, one accumulator row per thread (tile 0: warps 4-7, tile 1: warps 8-11):
 //                            tcgen05.ld 128 fp32, the 128-point Hadamard transform in the thread's registers,
 //                            scales, limited SwiGLU, down-input rotation; fp16 Xd rows (gate/up) or fp32 Y rows (down)
-//               warps 12-19  decode the trellis tiles of B (the weights) to fp16 straight into the swizzled K-major
+//               warps 12-27  decode the trellis tiles of B (the weights) to fp16 straight into the swizzled K-major
 //                            shared-memory tile (bit-exact codebook; conflict-free 32-bit stores); the packed words
 //                            of the next stage are already in registers while a stage is decoded
 //             A decoded B stage serves BOTH M tiles of the item (256 rows), which halves the decode work per
@@ -50,7 +50,22 @@ int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limi
 #ifndef FG_PROBE
 #define FG_PROBE 0
 #endif
-constexpr int FG_THREADS = 640;
+// FG_DEC_WARPS: trellis-decode warps per CTA (8 or 16).  With 16 (the default: the decode is what the kernel waits for,
+// and four instead of two decode warps per scheduler raise its issue rate; measured 0.90 -> 0.80 ms per layer) every
+// warp owns two n-tiles of a k-tile instead of four, the CTA has 896 threads, and the register pool (896 x 72) is
+// split 24 / 152 / 40 per thread over the producer, epilogue and decode warpgroups (8 warps: 40 / 152 / 64 of 640 x 96).
+#ifndef FG_DEC_WARPS
+#define FG_DEC_WARPS 16
+#endif
+#ifndef FG_EPI_REGS
+#define FG_EPI_REGS 152
+#endif
+#ifndef FG_DEC_REGS
+#define FG_DEC_REGS 40
+#endif
+#define FG_STR2(x) #x
+#define FG_STR(x) FG_STR2(x)
+constexpr int FG_THREADS = (12 + FG_DEC_WARPS) * 32;
 constexpr int FG_BM = 128, FG_BN = 128, FG_BK = 64;
 constexpr int FG_TILE_BYTES = FG_BM * FG_BK * 2;           // 16 KB: one 128 x 64 fp16 operand tile
 constexpr int FG_MAXU = 1024;
@@ -345,7 +360,7 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     unsigned char *stages = smem;
     uint32_t *gbuf = reinterpret_cast<uint32_t *>(smem + (size_t)C::STAGES * C::STAGE_BYTES); // [64][256]
     unsigned char *tables = smem + (size_t)C::STAGES * C::STAGE_BYTES + C::GBUF_BYTES;
-    uint64_t *full = reinterpret_cast<uint64_t *>(tables);                 // [STAGES] A landed (tx) + 8 decode warps
+    uint64_t *full = reinterpret_cast<uint64_t *>(tables);                 // [STAGES] A landed (tx) + the decode warps
     uint64_t *empty = full + C::STAGES;                                    // [STAGES] MMAs of the stage completed
     uint64_t *tmem_full = empty + C::STAGES;                               // [2] accumulators of a pass complete
     uint64_t *tmem_empty = tmem_full + 2;                                  // [2] accumulators drained (8 epilogue warps)
@@ -363,7 +378,7 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
     const int total = (pairs_all + a.plan[3]) * NB;
 
     if (tid == 0) {
-        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full + s, 9); mbar_init(empty + s, 1); }
+        for (int s = 0; s < C::STAGES; ++s) { mbar_init(full + s, 1 + FG_DEC_WARPS); mbar_init(empty + s, 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(tmem_full + b, 1); mbar_init(tmem_empty + b, 8); }
         *abort_flag = 0;
         mbar_fence_init();
@@ -380,7 +395,11 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
 
     if (warp < 4) {
         // ------------------------------------------------------------------ warpgroup 0: TMA, MMA issue
+#if FG_DEC_WARPS == 16
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 24;");
+#else
         asm volatile("setmaxnreg.dec.sync.aligned.u32 40;");
+#endif
         if (warp == 0 && lane == 0) {
             uint32_t it = 0;
             for (int item = blockIdx.x; item < total && !*abort_flag; item += gridDim.x) {
@@ -445,7 +464,11 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         }
     } else if (warp < 12) {
         // ------------------------------------------------------------------ warpgroups 1-2: epilogue (tile 0 | tile 1)
+#if FG_DEC_WARPS == 16
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 " FG_STR(FG_EPI_REGS) ";");
+#else
         asm volatile("setmaxnreg.inc.sync.aligned.u32 152;");
+#endif
         const int q = warp & 3, tl = (warp - 4) >> 2;        // TMEM lane quadrant, M tile of the item
         const int m = q * 32 + lane, em = tl * 128 + m;      // row of the tile, row of the item (0..255)
         uint32_t pc = 0;
@@ -547,10 +570,14 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         }
     } else {
         // ------------------------------------------------------------------ warpgroups 3-4: trellis decode of B
+#if FG_DEC_WARPS == 16
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 " FG_STR(FG_DEC_REGS) ";");
+#else
         asm volatile("setmaxnreg.dec.sync.aligned.u32 64;");
+#endif
         const int dw = warp - 12;
-        constexpr int NTL = 4;                               // n tiles of this warp per stage
-        const int ktl = dw & 3, nt_begin = (dw >> 2) * 4;
+        constexpr int NTL = 32 / FG_DEC_WARPS;               // n tiles of this warp per stage (4 k-tiles x 8 n-tiles in all)
+        const int ktl = dw & 3, nt_begin = (dw >> 2) * NTL;
         const int g = lane >> 2, tq = lane & 3;
         // byte offsets inside the B tile of this lane's four 32-bit stores (before the n-tile offset)
         const int c0 = 2 * ktl, c1 = 2 * ktl + 1;
