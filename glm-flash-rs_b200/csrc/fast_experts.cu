@@ -481,8 +481,10 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
             asm volatile("bar.sync 1, 256;");
             if (em < 128) {
                 const size_t o = (size_t)t.e * a.N + t.nb * 128 + em;
-                scales[em] = __half2float(a.sv0[o]);
-                if (MATS == 2) { scales[128 + em] = __half2float(a.sv1[o]); scales[256 + em] = __half2float(a.sd[o]); }
+                // the 1 / sqrt(128) of every Hadamard transform is folded into the scale vectors here (the transform is
+                // linear), which takes one multiply per element out of each epilogue step
+                scales[em] = __half2float(a.sv0[o]) * HAD_SCALE;
+                if (MATS == 2) { scales[128 + em] = __half2float(a.sv1[o]) * HAD_SCALE; scales[256 + em] = __half2float(a.sd[o]) * HAD_SCALE; }
             }
             asm volatile("bar.sync 1, 256;");
             float v[128];
@@ -509,8 +511,8 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                     // gate: scale, bf16 rounding, clamp, silu (rounded) -> two bf16 per word, this thread's column of gbuf
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
-                        const float g0 = fminf(bf16r(v[2 * i] * HAD_SCALE * scales[2 * i]), a.limit);
-                        const float g1 = fminf(bf16r(v[2 * i + 1] * HAD_SCALE * scales[2 * i + 1]), a.limit);
+                        const float g0 = fminf(bf16r(v[2 * i] * scales[2 * i]), a.limit);
+                        const float g1 = fminf(bf16r(v[2 * i + 1] * scales[2 * i + 1]), a.limit);
                         const float s0 = bf16r(__fdividef(g0, 1.f + __expf(-g0)));
                         const float s1 = bf16r(__fdividef(g1, 1.f + __expf(-g1)));
                         gbuf[i * 256 + em] = (__float_as_uint(s0) >> 16) | (__float_as_uint(s1) & 0xffff0000u);
@@ -519,8 +521,8 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
                         const uint32_t gp = gbuf[i * 256 + em];
-                        const float u0 = fminf(fmaxf(bf16r(v[2 * i] * HAD_SCALE * scales[128 + 2 * i]), -a.limit), a.limit);
-                        const float u1 = fminf(fmaxf(bf16r(v[2 * i + 1] * HAD_SCALE * scales[128 + 2 * i + 1]), -a.limit), a.limit);
+                        const float u0 = fminf(fmaxf(bf16r(v[2 * i] * scales[128 + 2 * i]), -a.limit), a.limit);
+                        const float u1 = fminf(fmaxf(bf16r(v[2 * i + 1] * scales[128 + 2 * i + 1]), -a.limit), a.limit);
                         v[2 * i] = bf16r(__uint_as_float(gp << 16) * u0) * scales[256 + 2 * i];
                         v[2 * i + 1] = bf16r(__uint_as_float(gp & 0xffff0000u) * u1) * scales[256 + 2 * i + 1];
                     }
@@ -532,8 +534,7 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                             __half2 h[4];
 #pragma unroll
                             for (int j = 0; j < 4; ++j)
-                                h[j] = __halves2half2(__float2half_rn(v[8 * c + 2 * j] * HAD_SCALE),
-                                                      __float2half_rn(v[8 * c + 2 * j + 1] * HAD_SCALE));
+                                h[j] = __halves2half2(__float2half_rn(v[8 * c + 2 * j]), __float2half_rn(v[8 * c + 2 * j + 1]));
                             o[c] = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
                                               *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
                         }
@@ -551,8 +552,8 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                         for (int c = 0; c < 4; ++c) {
                             const int col = ch * 16 + 4 * c;
                             *reinterpret_cast<float4 *>(wbuf + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) =
-                                make_float4(v[col] * HAD_SCALE * scales[col], v[col + 1] * HAD_SCALE * scales[col + 1],
-                                            v[col + 2] * HAD_SCALE * scales[col + 2], v[col + 3] * HAD_SCALE * scales[col + 3]);
+                                make_float4(v[col] * scales[col], v[col + 1] * scales[col + 1], v[col + 2] * scales[col + 2],
+                                            v[col + 3] * scales[col + 3]);
                         }
                         __syncwarp();
 #pragma unroll
