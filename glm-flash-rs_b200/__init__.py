@@ -51,6 +51,12 @@ SYMBOLS = {
     "glmflash_experts_xd": (_P, [_P]),
     "glmflash_experts_status": (_P, [_P]),
     "glmflash_experts_set_phases": (_I, [_P, _I]),
+    "glmflash_experts_clear_status": (_I, [_P, _P]),
+    "glmflash_fast_experts_clear_status": (_I, [_P, _P]),
+    "glmflash_moe_status": (_P, [_P]),
+    "glmflash_moe_clear_status": (_I, [_P, _P]),
+    "glmflash_moe_run_ep": (_I, [_P, _P, _P, _P, _P, _I, _P, _P, _I, _I]),
+    "glmflash_ep_clear_status": (_I, [_P, _P]),
     "glmflash_fast_experts_new": (_I, [_P, _Z, _P]),
     "glmflash_fast_experts_free": (None, [_P]),
     "glmflash_fast_experts_run": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I]),
@@ -178,7 +184,7 @@ def exl3_linear(x, words, suh, svh, K, N, stream=None):
 
 def exl3_linear_static(x, words, suh, svh, K, N, stream=None):
     """exl3_linear without any allocation inside the library: the scratch is the library's built-in array
-    (K <= 2048, N <= 2048).  Calls that overlap on the GPU share that array and must be ordered by the caller."""
+    (K <= 4096).  Calls that overlap on the GPU share that array and must be ordered by the caller."""
     torch = _torch()
     rows = x.shape[0]
     y = torch.empty((rows, N), dtype=torch.float16, device=x.device)
@@ -320,6 +326,21 @@ class Moe(_Owner):
     def set_phases(self, mask):
         _check(lib().glmflash_moe_set_phases(self._h, mask))
 
+    def run_ep(self, ep, w, x, picks, route_w, rows, shared_here=-1, x_stride=None, stream=None):
+        """The layer and its cross-GPU exchange (glmflash_moe_run_ep); result: ep.output[:rows]."""
+        ws = w if isinstance(w, Weights) else weights_struct(w)
+        _check(lib().glmflash_moe_run_ep(self._h, ep._h, _stream_ptr(stream), C.byref(ws), x.data_ptr(),
+                                         x_stride or x.stride(0), picks.data_ptr(), route_w.data_ptr(), rows, int(shared_here)))
+        return ep.output[:rows]
+
+    @property
+    def status(self):
+        import torch
+        return _view(lib().glmflash_moe_status(self._h), (1,), torch.int32)
+
+    def clear_status(self, stream=None):
+        _check(lib().glmflash_moe_clear_status(self._h, _stream_ptr(stream)))
+
     @property
     def pairs_ptr(self):
         """Device address of the pair results Y fp32 [rows*slots][H] of the last run."""
@@ -403,6 +424,9 @@ class EpCombine:
         """Same-process peers: `bases[k]` = local_base of rank k's owner."""
         arr = (C.c_void_p * self.world)(*[C.c_void_p(b) for b in bases])
         _check(lib().glmflash_ep_connect_ptrs(self._h, arr))
+
+    def clear_status(self, stream=None):
+        _check(lib().glmflash_ep_clear_status(self._h, _stream_ptr(stream)))
 
     def set_wait_limit(self, polls):
         _check(lib().glmflash_ep_set_wait_limit(self._h, polls))

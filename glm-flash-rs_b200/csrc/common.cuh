@@ -166,8 +166,9 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parit
 // Bounded wait: gives up after `limit` polls and reports false (the caller records an error status and
 // leaves); nothing in this library spins without a bound.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = 4000000u) {
-    for (uint32_t i = 0; i < limit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait(bar, parity)) return true;
+    for (uint32_t i = 0; i < limit; ++i)              // the waiting thread may sleep inside the instruction: no issue slots taken
+        if (mbar_try_wait_hint(bar, parity, 400u)) return true;
     return false;
 }
 // 1-D TMA bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses and the

@@ -21,9 +21,9 @@
 #include <vector>
 
 #include "common.cuh"
+#include "owners.cuh"
 
 namespace gf {
-int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
 
 constexpr int EP_MAX_WORLD = 8;
 constexpr int EP_THREADS = 256;
@@ -213,7 +213,8 @@ struct glmflash_ep {
     glmflash_config cfg;
     int rank = 0, world = 1, max_ctas = 0;
     unsigned char *local = nullptr;               // one allocation: recv | flags | epoch | done | status
-    size_t recv_bytes = 0, flag_bytes = 0, fin_bytes = 0, fin_flag_bytes = 0, total_bytes = 0;
+    size_t recv_bytes = 0, flag_bytes = 0, fin_bytes = 0, fin_flag_bytes = 0, win_flag_bytes = 0, total_bytes = 0;
+    size_t tail() const { return recv_bytes + flag_bytes + fin_bytes + fin_flag_bytes + win_flag_bytes; }   // epoch | done | status
     void *peer_base[EP_MAX_WORLD] = {};
     bool opened[EP_MAX_WORLD] = {};
     bool connected = false;
@@ -221,7 +222,23 @@ struct glmflash_ep {
     unsigned wait_polls = 2000000u;               // about a second of polling before a wait gives up
 };
 
-extern "C" size_t glmflash_ep_handle_bytes(void) { return sizeof(cudaIpcMemHandle_t); }
+// What a rank publishes: the IPC handle of its receive area and a hash of everything the peers' address arithmetic
+// depends on.  Upstream makes its ranks agree on their configuration with control records before the first exchange
+// (src/comm.rs:66-96, src/model.rs:259-315); here the agreement rides on the bootstrap blob.
+struct EpBlob {
+    cudaIpcMemHandle_t mem;
+    uint64_t config_hash;
+};
+static uint64_t ep_config_hash(const glmflash_config &c, int world) {
+    const int32_t f[8] = {GLMFLASH_ABI_VERSION, c.hidden, c.inter, c.experts, c.slots, c.max_rows, world, EP_THREADS};
+    uint64_t h = 1469598103934665603ull;                      // FNV-1a
+    for (size_t i = 0; i < sizeof(f); ++i) {
+        h ^= reinterpret_cast<const unsigned char *>(f)[i];
+        h *= 1099511628211ull;
+    }
+    return h;
+}
+extern "C" size_t glmflash_ep_handle_bytes(void) { return sizeof(EpBlob); }
 
 extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int rank, int world, glmflash_ep **out) {
     GF_REQUIRE(out != nullptr, "out is null");
@@ -237,7 +254,9 @@ extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int
     h->flag_bytes = ((size_t)2 * world * h->max_ctas * 4 + 255) / 256 * 256;
     h->fin_bytes = R > 16 ? (size_t)2 * R * H * 4 : 0;        // the two-step form serves windows of more than 16 rows
     h->fin_flag_bytes = R > 16 ? ((size_t)2 * h->max_ctas * 4 + 255) / 256 * 256 : 0;
-    h->total_bytes = h->recv_bytes + h->flag_bytes + h->fin_bytes + h->fin_flag_bytes + 256;
+    // arrival words of the one-launch layer kernel's exchange (windows of <= 16 rows): [2][world][R][H / 128]
+    h->win_flag_bytes = R <= 16 ? ((size_t)2 * world * R * (H / 128) * 4 + 255) / 256 * 256 : 0;
+    h->total_bytes = h->tail() + 256;
     if (cudaMalloc((void **)&h->local, h->total_bytes) != cudaSuccess || cudaMemset(h->local, 0, h->total_bytes) != cudaSuccess ||
         cudaMalloc((void **)&h->out, R * H * 4) != cudaSuccess) {
         glmflash_ep_free(h);
@@ -259,9 +278,10 @@ extern "C" void glmflash_ep_free(glmflash_ep *h) {
 
 extern "C" int glmflash_ep_get_handle(glmflash_ep *h, void *handle_out) {
     GF_REQUIRE(h && handle_out, "null argument");
-    cudaIpcMemHandle_t m;
-    GF_CUDA(cudaIpcGetMemHandle(&m, h->local));
-    memcpy(handle_out, &m, sizeof(m));
+    EpBlob b{};
+    GF_CUDA(cudaIpcGetMemHandle(&b.mem, h->local));
+    b.config_hash = ep_config_hash(h->cfg, h->world);
+    memcpy(handle_out, &b, sizeof(b));
     return 0;
 }
 
@@ -269,10 +289,18 @@ extern "C" int glmflash_ep_connect(glmflash_ep *h, const void *all_handles) {
     GF_REQUIRE(h && all_handles, "null argument");
     GF_REQUIRE(!h->connected, "already connected");
     const unsigned char *p = (const unsigned char *)all_handles;
+    const uint64_t mine = ep_config_hash(h->cfg, h->world);
+    for (int k = 0; k < h->world; ++k) {                      // every rank's blob is checked before any mapping is made
+        EpBlob b;
+        memcpy(&b, p + (size_t)k * sizeof(b), sizeof(b));
+        GF_REQUIRE(b.config_hash == mine, "rank " + std::to_string(k) + " was built with a different configuration "
+                   "(hidden / inter / experts / slots / max_rows / world must agree on every rank)");
+    }
     for (int k = 0; k < h->world; ++k) {
         if (k == h->rank) continue;
-        cudaIpcMemHandle_t m;
-        memcpy(&m, p + (size_t)k * sizeof(m), sizeof(m));
+        EpBlob b;
+        memcpy(&b, p + (size_t)k * sizeof(b), sizeof(b));
+        const cudaIpcMemHandle_t m = b.mem;
         void *base = nullptr;
         GF_CUDA(cudaIpcOpenMemHandle(&base, m, cudaIpcMemLazyEnablePeerAccess));
         h->peer_base[k] = base;
@@ -295,7 +323,7 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
         peers.fin[k] = (float *)((unsigned char *)h->peer_base[k] + h->recv_bytes + h->flag_bytes);
         peers.fin_flags[k] = (unsigned *)((unsigned char *)h->peer_base[k] + h->recv_bytes + h->flag_bytes + h->fin_bytes);
     }
-    unsigned *epoch = (unsigned *)(h->local + h->recv_bytes + h->flag_bytes + h->fin_bytes + h->fin_flag_bytes);
+    unsigned *epoch = (unsigned *)(h->local + h->tail());
     const dim3 grid((unsigned)((c.hidden / 4 + EP_THREADS - 1) / EP_THREADS), (unsigned)rows);
     if (rows > 16 && h->world > 1)
         return launch_k(ep_exchange_rows_kernel, dim3((unsigned)((rows + EP_RB - 1) / EP_RB)), dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w,
@@ -330,5 +358,31 @@ extern "C" int glmflash_ep_connect_ptrs(glmflash_ep *h, void *const *peer_bases)
 
 extern "C" float *glmflash_ep_output(const glmflash_ep *h) { return h ? h->out : nullptr; }
 extern "C" const int32_t *glmflash_ep_status(const glmflash_ep *h) {
-    return h ? (const int32_t *)(h->local + h->recv_bytes + h->flag_bytes + h->fin_bytes + h->fin_flag_bytes + 8) : nullptr;
+    return h ? (const int32_t *)(h->local + h->tail() + 8) : nullptr;
 }
+// After a peer time-out the status word stays set and every later wait gives up early, so that a dead peer costs one
+// time-out and not one per block; the host clears it here when it has dealt with the failure.
+extern "C" int glmflash_ep_clear_status(glmflash_ep *h, void *stream) {
+    GF_REQUIRE(h != nullptr, "null argument");
+    GF_CUDA(cudaMemsetAsync(h->local + h->tail() + 8, 0, 4, (cudaStream_t)stream));
+    return 0;
+}
+
+namespace gf {
+// The peer table of the one-launch layer kernel's exchange (window.cu).
+int ep_window_peers(glmflash_ep *h, WinPeers *out, float **result) {
+    GF_REQUIRE(h && out && result, "null argument");
+    GF_REQUIRE(h->connected, "glmflash_ep_connect has not been called");
+    GF_REQUIRE(h->win_flag_bytes > 0, "this exchange owner was built for more than 16 rows");
+    *out = WinPeers{};
+    for (int k = 0; k < h->world; ++k) {
+        out->recv[k] = (float *)h->peer_base[k];
+        out->flags[k] = (unsigned *)((unsigned char *)h->peer_base[k] + h->recv_bytes + h->flag_bytes + h->fin_bytes + h->fin_flag_bytes);
+    }
+    out->rank = h->rank; out->world = h->world; out->max_rows = h->cfg.max_rows; out->wait_polls = h->wait_polls;
+    out->epoch = (unsigned *)(h->local + h->tail());
+    out->status = (int *)(h->local + h->tail() + 8);
+    *result = h->out;
+    return 0;
+}
+}  // namespace gf

@@ -3,8 +3,10 @@
 #include <new>
 
 #include "gemv.cuh"
+#include "owners.cuh"
 
 namespace gf {
+size_t experts_window_sync_words(const glmflash_config &c);
 
 template <typename F>
 static int set_smem(F *kernel, size_t bytes) {
@@ -27,6 +29,8 @@ int launch_rot_in(cudaStream_t s, const void *x, bool x_is_bf16, int x_stride, c
 int launch_gemv(cudaStream_t s, int mats, GemvArgs a, int umax, bool pdl) {
     const int sets = a.maxm > 8 ? 2 : 1;
     gemv_split(a.K, a.KTC, a.SK);
+    GF_REQUIRE(a.SK * a.KTC == a.K / 16 && a.KTC % 8 == 0, "K cannot be cut into whole 128-k blocks per split");
+    GF_REQUIRE(a.KTC <= 64, "K is too large for the decode path (at most 16 copy barriers per CTA)");
     const size_t smem = gemv_smem_bytes(mats, sets, a.KTC);
     GF_REQUIRE(smem <= 200 * 1024, "K is too large for the decode path's shared-memory staging");
     static size_t configured[64][4] = {};
@@ -69,14 +73,6 @@ int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limi
 
 using namespace gf;
 
-struct glmflash_experts {
-    glmflash_config cfg;
-    __half *xg = nullptr, *xu = nullptr, *xd = nullptr;
-    float *y = nullptr;
-    int *status = nullptr;
-    int phases = 7;                                 // profiling aid: 1 = input rotation, 2 = gate/up, 4 = down
-};
-
 extern "C" int glmflash_experts_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_experts **out) {
     GF_REQUIRE(out != nullptr, "out is null");
     *out = nullptr;
@@ -90,8 +86,11 @@ extern "C" int glmflash_experts_new(const glmflash_config *cfg, size_t cfg_bytes
         GF_CUDA(cudaMemset(*p, 0, bytes));
         return 0;
     };
+    e->sync_words = experts_window_sync_words(*cfg);
     if (alloc((void **)&e->xg, P * H * 2) || alloc((void **)&e->xu, P * H * 2) || alloc((void **)&e->xd, P * I * 2) ||
-        alloc((void **)&e->y, P * H * 4) || alloc((void **)&e->status, 4)) {
+        alloc((void **)&e->y, P * H * 4) || alloc((void **)&e->status, 4) ||
+        alloc((void **)&e->z1, (size_t)2 * (H / 128) * P * I * 4) || alloc((void **)&e->z2, (size_t)(I / 128) * P * H * 4) ||
+        alloc((void **)&e->sync, e->sync_words * 4) || alloc((void **)&e->out, (size_t)cfg->max_rows * H * 4)) {
         glmflash_experts_free(e);
         return -1;
     }
@@ -102,6 +101,7 @@ extern "C" int glmflash_experts_new(const glmflash_config *cfg, size_t cfg_bytes
 extern "C" void glmflash_experts_free(glmflash_experts *e) {
     if (!e) return;
     cudaFree(e->xg); cudaFree(e->xu); cudaFree(e->xd); cudaFree(e->y); cudaFree(e->status);
+    cudaFree(e->z1); cudaFree(e->z2); cudaFree(e->sync); cudaFree(e->out);
     delete e;
 }
 
@@ -187,6 +187,13 @@ extern "C" int glmflash_experts_set_phases(glmflash_experts *e, int mask) {
 extern "C" float *glmflash_experts_y(const glmflash_experts *e) { return e ? e->y : nullptr; }
 extern "C" const uint16_t *glmflash_experts_xd(const glmflash_experts *e) { return e ? (const uint16_t *)e->xd : nullptr; }
 extern "C" const int32_t *glmflash_experts_status(const glmflash_experts *e) { return e ? e->status : nullptr; }
+extern "C" int glmflash_experts_clear_status(glmflash_experts *e, void *stream) {
+    GF_REQUIRE(e != nullptr, "null argument");
+    // a give-up may have left arrival counters of the one-launch kernel half way: clear them with the status word
+    GF_CUDA(cudaMemsetAsync(e->status, 0, 4, (cudaStream_t)stream));
+    GF_CUDA(cudaMemsetAsync(e->sync, 0, e->sync_words * 4, (cudaStream_t)stream));
+    return 0;
+}
 
 // ---- single EXL3 linear (fp16 in, fp16 out): rot_in + one-matrix GEMV with the fp16 epilogue ---------------
 namespace {

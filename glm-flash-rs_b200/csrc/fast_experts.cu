@@ -745,7 +745,7 @@ extern "C" int glmflash_fast_experts_new(const glmflash_config *cfg, size_t cfg_
     }
     if (alloc((void **)&f->xg, P * H * 2) || alloc((void **)&f->xu, P * H * 2) || alloc((void **)&f->xd, P * I * 2) ||
         alloc((void **)&f->out, P * H * 4) || alloc((void **)&f->plan, PLAN_INTS * 4) || alloc((void **)&f->src_pair, P * 4) ||
-        alloc((void **)&f->row_expert, P * 4) || alloc((void **)&f->status, 4) || make_map(&f->map_xg, f->xg, P, H) ||
+        alloc((void **)&f->row_expert, P * 4) || alloc((void **)&f->status, 16) || make_map(&f->map_xg, f->xg, P, H) ||
         make_map(&f->map_xu, f->xu, P, H) || make_map(&f->map_xd, f->xd, P, I) ||
         fail_if(cudaFuncSetAttribute(fast_gemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FgCfg<2>::SMEM)) ||
         fail_if(cudaFuncSetAttribute(fast_gemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)FgCfg<1>::SMEM))) {
@@ -808,3 +808,8 @@ extern "C" const uint16_t *glmflash_fast_experts_xd(const glmflash_fast_experts 
 extern "C" const int32_t *glmflash_fast_experts_row_pairs(const glmflash_fast_experts *f) { return f ? f->src_pair : nullptr; }
 extern "C" const int32_t *glmflash_fast_experts_plan(const glmflash_fast_experts *f) { return f ? f->plan : nullptr; }
 extern "C" const int32_t *glmflash_fast_experts_status(const glmflash_fast_experts *f) { return f ? f->status : nullptr; }
+extern "C" int glmflash_fast_experts_clear_status(glmflash_fast_experts *f, void *stream) {
+    GF_REQUIRE(f != nullptr, "null argument");
+    GF_CUDA(cudaMemsetAsync(f->status, 0, 4, (cudaStream_t)stream));
+    return 0;
+}

@@ -118,11 +118,18 @@ __device__ __forceinline__ uint32_t weight_dup(uint32_t x) {
     return *reinterpret_cast<const uint32_t *>(&r);
 }
 
-// K split of a shape: k-tiles per CTA (a multiple of 16) and the number of splits (<= 8, the cluster size)
+// K split of a shape: k-tiles per CTA and the number of splits (<= 8, the cluster size); sk * ktc == K / 16 always.
+// Powers of two times 16 k-tiles where that divides K / 16 (2048: 8 x 16, 1536: 6 x 16, 4096: 8 x 32); other multiples
+// of 256 take the largest split count whose share is a whole number of 128-k Hadamard blocks (2304: 6 x 24).
 inline void gemv_split(int K, int &ktc, int &sk) {
+    const int KT = K / 16;
     ktc = 16;
-    while ((K / 16) / ktc > GEMV_MAX_SPLITS) ktc *= 2;
-    sk = (K / 16) / ktc;
+    while (KT / ktc > GEMV_MAX_SPLITS) ktc *= 2;
+    sk = KT / ktc;
+    if (sk * ktc == KT) return;
+    for (sk = GEMV_MAX_SPLITS; sk > 1; --sk)
+        if (KT % sk == 0 && (KT / sk) % 8 == 0) break;
+    ktc = KT / sk;
 }
 // dynamic shared memory size of a launch
 inline size_t gemv_smem_bytes(int mats, int sets, int ktc) {

@@ -4,12 +4,11 @@
 #include <algorithm>
 #include <new>
 
-#include "common.cuh"
+#include <stdlib.h>
 
-namespace gf {
-int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limit);
-}
-struct glmflash_experts;
+#include "common.cuh"
+#include "owners.cuh"
+
 namespace gf {
 int experts_run_fused(glmflash_experts *e, cudaStream_t s, const glmflash_weights *w, const void *input, int x_stride,
                       const int32_t *picks, int rows);
@@ -90,6 +89,7 @@ struct glmflash_moe {
     int *picks_dev = nullptr;
     float *w_dev = nullptr;
     int phases = 31;                                // profiling aid, see glmflash_moe_set_phases
+    bool one_launch = false;                        // windows of <= 16 rows: the one-launch layer kernel (window.cu)
 };
 
 extern "C" int glmflash_moe_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_moe **out) {
@@ -112,6 +112,10 @@ extern "C" int glmflash_moe_new(const glmflash_config *cfg, size_t cfg_bytes, gl
         return -1;
     }
     cudaMemset(m->out, 0, rows * cfg->hidden * 4);
+    // Windows of <= 16 rows: three launches per layer (gate/up, down, combine) by default; GLMFLASH_LAYER_KERNELS=1
+    // selects the one-launch layer kernel (window.cu), which measured slower on one GPU (43 vs 28 us per one-token layer)
+    const char *env = getenv("GLMFLASH_LAYER_KERNELS");
+    m->one_launch = env && env[0] == '1';
     *out = m;
     return 0;
 }
@@ -130,8 +134,11 @@ extern "C" int glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_we
     GF_REQUIRE(m && w && input && picks && route_w, "null argument");
     GF_REQUIRE(rows > 0 && rows <= m->cfg.max_rows, "rows outside the scratch bound");
     const float *Y;
+    if (m->experts && m->one_launch && m->phases == 31 && experts_window_supported(m->cfg, rows))
+        // windows of <= 16 rows: grouping, rotation, both projections, epilogues and the combine in one launch
+        return experts_run_window(m->experts, (cudaStream_t)stream, w, input, x_stride, picks, route_w, rows, m->out, nullptr, -1);
     if (m->experts) {
-        // windows of <= 16 rows: grouping and input rotation happen inside the expert kernels
+        // the same as three launches: grouping and input rotation happen inside the expert kernels
         if (experts_run_fused(m->experts, (cudaStream_t)stream, w, input, x_stride, picks, rows)) return -1;
         Y = glmflash_experts_y(m->experts);
     } else {
@@ -147,6 +154,29 @@ extern "C" int glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_we
     return launch_combine((cudaStream_t)stream, Y, picks, route_w, m->out, rows, m->cfg);
 }
 
+// Expert-parallel form of glmflash_moe_run.  Windows of <= 16 rows: the layer kernel itself pushes each finished block
+// of this rank's partial into every peer's receive slot and adds the ranks' slots in rank order (one launch per
+// layer and rank); larger windows: the experts of this rank, then the exchange kernel of the owner.
+extern "C" int glmflash_moe_run_ep(glmflash_moe *m, glmflash_ep *ep, void *stream, const glmflash_weights *w, const void *input,
+                                   int x_stride, const int32_t *picks, const float *route_w, int rows, int shared_here) {
+    GF_REQUIRE(m && ep && w && input && picks && route_w, "null argument");
+    GF_REQUIRE(rows > 0 && rows <= m->cfg.max_rows, "rows outside the scratch bound");
+    if (m->experts && m->one_launch && experts_window_supported(m->cfg, rows)) {
+        WinPeers peers;
+        float *result = nullptr;
+        if (ep_window_peers(ep, &peers, &result)) return -1;
+        GF_REQUIRE(peers.max_rows == m->cfg.max_rows, "the layer owner and the exchange owner were built for different row counts");
+        return experts_run_window(m->experts, (cudaStream_t)stream, w, input, x_stride, picks, route_w, rows, result,
+                                  peers.world > 1 ? &peers : nullptr, shared_here);
+    }
+    const int saved = m->phases;
+    m->phases &= ~16;                               // experts only: the combine is the exchange kernel's first step
+    const int rc = glmflash_moe_run(m, stream, w, input, x_stride, picks, route_w, rows);
+    m->phases = saved;
+    if (rc) return -1;
+    return glmflash_ep_combine(ep, stream, glmflash_moe_pairs(m), picks, route_w, rows, shared_here < 0 ? m->cfg.shared_exl3 : shared_here);
+}
+
 extern "C" int glmflash_moe_set_phases(glmflash_moe *m, int mask) {
     GF_REQUIRE(m != nullptr, "null argument");
     m->phases = mask;
@@ -155,6 +185,14 @@ extern "C" int glmflash_moe_set_phases(glmflash_moe *m, int mask) {
 }
 
 extern "C" float *glmflash_moe_output(const glmflash_moe *m) { return m ? m->out : nullptr; }
+extern "C" const int32_t *glmflash_moe_status(const glmflash_moe *m) {
+    if (!m) return nullptr;
+    return m->experts ? glmflash_experts_status(m->experts) : glmflash_fast_experts_status(m->fast);
+}
+extern "C" int glmflash_moe_clear_status(glmflash_moe *m, void *stream) {
+    GF_REQUIRE(m != nullptr, "null argument");
+    return m->experts ? glmflash_experts_clear_status(m->experts, stream) : glmflash_fast_experts_clear_status(m->fast, stream);
+}
 extern "C" const float *glmflash_moe_pairs(const glmflash_moe *m) {
     if (!m) return nullptr;
     return m->experts ? glmflash_experts_y(m->experts) : glmflash_fast_experts_output(m->fast);

@@ -79,6 +79,7 @@ class EpMoe:
         self.pkg, self.rank, self.world, self.group = pkg, rank, world, group
         self.experts, self.hidden, self.exchange = experts, hidden, exchange if world > 1 else "none"
         lo, hi = expert_window(rank, world, experts)
+        self.window = (lo, hi)
         self.row_split = world > 1 and max_rows > 16           # prefill: the shared expert is split by rows
         srows = shared_rows(rank, world, max_rows) if self.row_split else (0, 0)
         kinds = (1,) if world == 1 or self.row_split else (0, 1)
@@ -95,8 +96,6 @@ class EpMoe:
             cfg = pkg.make_config(hidden, inter, experts, slots, max_rows=max_rows, shared_exl3=0, expert_lo=lo, expert_hi=hi,
                                   shared_rows=srows)
             self.ep = pkg.EpCombine(cfg, rank, world, gather)
-            for m in self.moes.values():
-                m.set_phases(15)                    # experts only: the combine is the fused exchange kernel's first step
 
     def owns_shared(self, layer):
         return self.world == 1 or self.row_split or shared_owner(layer, self.world) == self.rank
@@ -106,16 +105,27 @@ class EpMoe:
 
     def run(self, layer, w, x, picks, route_w, rows, out=None, stream=None):
         m = self.owner(layer)
-        m.run(w, x, picks, route_w, rows, stream=stream)
-        if self.exchange == "none":
-            return m.output[:rows]
         if self.exchange == "nvlink":
-            res = self.ep.combine(m.pairs_ptr, picks, route_w, rows, self.owns_shared(layer), stream=stream)
+            # one call: the layer and its exchange (windows of <= 16 rows: one launch per rank)
+            res = m.run_ep(self.ep, w, x, picks, route_w, rows, shared_here=self.owns_shared(layer), stream=stream)
             if out is not None:
                 out.copy_(res)
                 return out
             return res
+        m.run(w, x, picks, route_w, rows, stream=stream)
+        if self.exchange == "none":
+            return m.output[:rows]
         out = self.final[:rows] if out is None else out
         g = self.gathered if rows == self.gathered.shape[1] else \
             self.gathered.view(-1)[: self.world * rows * self.hidden].view(self.world, rows, self.hidden)
         return exchange(m.output[:rows], g, out, self.group, lambda a, b: self.pkg.rank_sum(a, b, stream=stream))
+
+    def check(self):
+        """Raises when a bounded wait inside a kernel gave up since the last check (call after synchronising)."""
+        import torch
+        torch.cuda.synchronize()
+        bad = {k: int(m.status.cpu()[0]) for k, m in self.moes.items() if int(m.status.cpu()[0])}
+        if self.exchange == "nvlink" and int(self.ep.status.cpu()[0]):
+            bad["exchange"] = int(self.ep.status.cpu()[0])
+        if bad:
+            raise self.pkg.GlmFlashError(f"device status words are set: {bad}")

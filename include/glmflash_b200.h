@@ -131,6 +131,10 @@ const uint16_t *glmflash_experts_xd(const glmflash_experts *e);
 /* Device status word (int32): 0 after a clean run; non-zero when a bounded wait inside a kernel gave up
  * (the analogue of upstream's poison word, native/roce.cu:127-141).  Read it after synchronising. */
 const int32_t *glmflash_experts_status(const glmflash_experts *e);
+/* Clears the status word (and the arrival counters a give-up may have left half way), in stream order: the way back
+ * to a usable owner after a bounded wait ran out (upstream rebuilds its transport after a poisoned exchange,
+ * src/roce.rs:275-282). */
+int  glmflash_experts_clear_status(glmflash_experts *e, void *stream);
 /* Profiling aid in the spirit of upstream's PROBE modes (native/expert_loads.cu:46-47): run only the selected
  * kernels of the pipeline (1 = input rotation, 2 = gate/up GEMV + SwiGLU epilogue, 4 = down GEMV + epilogue;
  * default 7).  Skipped phases leave the scratch of the previous run in place; results are then meaningless. */
@@ -155,13 +159,18 @@ const int32_t *glmflash_fast_experts_row_pairs(const glmflash_fast_experts *f);
 const int32_t *glmflash_fast_experts_plan(const glmflash_fast_experts *f);
 /* Device status word, as glmflash_experts_status. */
 const int32_t *glmflash_fast_experts_status(const glmflash_fast_experts *f);
+int  glmflash_fast_experts_clear_status(glmflash_fast_experts *f, void *stream);
 /* Profiling aid, as glmflash_experts_set_phases: 1 = plan, 2 = input rotation, 4 = gate/up GEMM, 8 = down GEMM
  * (default 15). */
 int  glmflash_fast_experts_set_phases(glmflash_fast_experts *f, int mask);
 
 /* ---- Moe: the whole layer after routing  (src/moe.rs:11-182, src/batch.rs:1160-1210) ---------------- */
 typedef struct glmflash_moe glmflash_moe;
-/* max_rows <= 16 builds the decode / verify pipeline, larger the prefill pipeline. */
+/* max_rows <= 16 builds the decode / verify pipeline, larger the prefill pipeline.
+ * Windows of <= 16 rows run as three launches per layer (gate/up with grouping and input rotation inside, down,
+ * combine: upstream's router-to-combine sequence src/moe.rs:101-181 in three kernels instead of eight).  With the
+ * environment variable GLMFLASH_LAYER_KERNELS=1 (read at construction) they run as ONE kernel per layer, which also
+ * carries the cross-GPU exchange of glmflash_moe_run_ep; on one GPU it measured slower than the three launches. */
 int  glmflash_moe_new(const glmflash_config *cfg, size_t cfg_bytes, glmflash_moe **out);
 void glmflash_moe_free(glmflash_moe *m);
 /* group -> routed and shared experts -> combine:
@@ -173,6 +182,10 @@ int  glmflash_moe_run(glmflash_moe *m, void *stream, const glmflash_weights *w, 
 float *glmflash_moe_output(const glmflash_moe *m);
 /* The pair results Y fp32 [rows*slots][H] behind the last run (the ExpertGpu / FastExperts output of this owner). */
 const float *glmflash_moe_pairs(const glmflash_moe *m);
+/* Device status word of the owner behind this layer (glmflash_experts_status / glmflash_fast_experts_status), and its
+ * reset. */
+const int32_t *glmflash_moe_status(const glmflash_moe *m);
+int  glmflash_moe_clear_status(glmflash_moe *m, void *stream);
 /* Profiling aid: 1 = grouping, 2 / 4 / 8 = the three ExpertGpu phases above, 16 = combine (default 31).  For
  * windows of <= 16 rows grouping and input rotation are fused into the gate/up kernel (bits 1 and 2 select nothing). */
 int  glmflash_moe_set_phases(glmflash_moe *m, int mask);
@@ -189,7 +202,9 @@ int  glmflash_moe_run_host(glmflash_moe *m, void *stream, const glmflash_weights
  * memory, plain stores), signal, wait (bounded) for the peers' partials and add the slots in rank order.
  * Set-up mirrors upstream's bootstrap (src/comm.rs:109-162): every rank creates its owner, publishes an opaque
  * handle of glmflash_ep_handle_bytes() bytes, receives all ranks' handles (in rank order, by whatever channel the
- * host has: TCP, torch.distributed, ...) and calls glmflash_ep_connect once.  Every rank must then call
+ * host has: TCP, torch.distributed, ...) and calls glmflash_ep_connect once.  The handle carries a hash of the sizes the
+ * peers' address arithmetic depends on (hidden, inter, experts, slots, max_rows, world): connect fails, before mapping
+ * anything, when a rank was built differently (upstream's config agreement, src/comm.rs:66-96, src/model.rs:259-315).  Every rank must then call
  * glmflash_ep_combine the same number of times in the same order.  A peer that never arrives makes the wait give up
  * after a bounded number of polls: the status word becomes non-zero and the output of that call is undefined. */
 typedef struct glmflash_ep glmflash_ep;
@@ -204,7 +219,18 @@ int  glmflash_ep_connect(glmflash_ep *h, const void *all_handles /* world x hand
 int  glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y, const int32_t *picks, const float *route_w, int rows,
                          int shared_here);
 float *glmflash_ep_output(const glmflash_ep *h);
+/* The layer and its exchange in one call (upstream: Moe::run_prefetched followed by finish(), src/model.rs:634-639).
+ * With the one-launch layer kernel selected (GLMFLASH_LAYER_KERNELS=1) windows of <= 16 rows take ONE launch per rank:
+ * the layer kernel stores each finished 128-column block of this rank's partial straight into every peer's receive slot
+ * and adds the ranks' slots in rank order itself; otherwise, and for larger windows, the experts run and then
+ * glmflash_ep_combine.  shared_here: 1 / 0 = this rank computes / skips the shared
+ * expert in this call, -1 = as the layer owner's config says.  Result: glmflash_ep_output(). */
+int  glmflash_moe_run_ep(glmflash_moe *m, glmflash_ep *ep, void *stream, const glmflash_weights *w, const void *input,
+                         int x_stride, const int32_t *picks, const float *route_w, int rows, int shared_here);
 const int32_t *glmflash_ep_status(const glmflash_ep *h);
+/* A peer time-out leaves the status word set, and while it is set every later wait gives up at once (a dead peer costs
+ * one time-out, not one per block).  Clear it, in stream order, once the host has dealt with the failure. */
+int  glmflash_ep_clear_status(glmflash_ep *h, void *stream);
 /* Number of polls after which a wait for a peer gives up (default 2,000,000, about a second). */
 int  glmflash_ep_set_wait_limit(glmflash_ep *h, uint32_t polls);
 /* For a host that drives several GPUs from ONE process (peer access enabled by the host): connect with the peers'

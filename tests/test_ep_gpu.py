@@ -105,7 +105,7 @@ def test_peer_that_never_arrives_times_out(pkg, synth, cuda):
     # the context is alive and the protocol recovers: rank 1 delivers the missed epoch, then both run a fresh one
     eps[1].combine(C_void(Y), pd, wd, rows, False)
     torch.cuda.synchronize()
-    eps[0].status.zero_()
+    eps[0].clear_status()                                       # the host has dealt with the failure
     eps[0].set_wait_limit(2000000)
     eps[1].set_wait_limit(20000)
     eps[1].combine(C_void(Y), pd, wd, rows, False)               # rank 1 pushes epoch 2 (its own wait for rank 0 runs out)
