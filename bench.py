@@ -13,14 +13,14 @@ input row and routing table, as the stack is "experts only").
     e2e      = the same through the public C-ABI calls with HOST buffers: per step the pinned host inputs of all layers
                are copied in, the layer calls run, all layer outputs are copied back, one synchronise; the blocking
                per-layer host-buffer call (glmflash_moe_run_host) is reported beside it as e2e_per_layer_host_call.
-    roofline = the dominant kernel (windows of <= 16 rows: the one-launch layer kernel; prefill: the gate/up grouped
+    roofline = the dominant kernel (windows of <= 16 rows: the gate/up grouped GEMV; prefill: the gate/up grouped
                GEMM) timed with CUDA events: algorithmic bytes (or flops) per launch / average duration / measured peak.
     workloads= the other benchmark configs in the same line: decode / verify windows of 4, 8 and 16 tokens (config 3
                routing: one bias vector shared by the tokens of a window) and the 4096-token prefill chunk (config 4),
                each with ms_per_step, value, e2e and its own roofline.
 N > 1: the 64 routed experts are split evenly over the ranks (expert parallel), the shared expert goes round robin over
 the layers (prefill: split by rows); every rank computes a partial layer output, and the ranks' partials are exchanged
-over NVLink and added in rank order (the reference's fixed-order sum after its all-gather), fused into the layer kernel.
+over NVLink and added in rank order (the reference's fixed-order sum after its all-gather) by the exchange kernel.
 Total work is fixed: "scaling": "strong".  Outside the timed region every rank also runs the whole window on its own and
 compares (ep_check); a failed check or a non-zero device status word makes the run exit non-zero.
 --impl reference: the reference's CPU path for the op (its scalar oracle restated in oracle/exl3_oracle.c; the Rust
@@ -44,6 +44,7 @@ import __graft_entry__ as entry  # noqa: E402
 H, I, E, S = 2048, 1536, 64, 5
 MAT_BYTES = H * I // 2                                     # packed bytes of one matrix
 W_E = 3 * MAT_BYTES + (2 * H + 2 * I + I + H) * 2          # 4,740,096 B: one expert's matrices + its six scale vectors
+GATEUP_BYTES_E = 2 * MAT_BYTES + (2 * H + 3 * I) * 2       # what the gate/up kernel reads per expert (algorithmic)
 INSTRUCTION_CEILING_GBS = 3800.0                           # packed bytes/s at one decode instruction per cycle and scheduler
 
 
@@ -343,15 +344,36 @@ class Bench:
         distinct = float(np.mean([len(np.unique(ps[l])) for l in range(L)]))          # experts touched incl. the shared one
         layer_bytes = distinct * W_E + rows * H * 6
         one_launch = os.environ.get("GLMFLASH_LAYER_KERNELS", "") == "1"
-        if G == 1:
+        if G == 1 and one_launch:
             gbs = layer_bytes / (ms_step / L * 1e-3) / 1e9
             res["roofline"] = {"bound": "hbm", "kernel": "window_kernel (grouping, input rotation, gate/up and down GEMV, SwiGLU and output "
-                               "epilogues, combine: the whole layer in one launch)" if one_launch else
-                               "the layer's three launches together: gemv_kernel<2,*> (gate/up + grouping + rotation + SwiGLU), gemv_kernel<1,*> (down), combine_kernel",
+                               "epilogues, combine: the whole layer in one launch)",
                                "achieved": gbs, "peak": self.peaks["hbm_gbs"], "peak_source": self.peaks["source"] + " hbm_gbs", "unit": "GB/s",
                                "frac": gbs / self.peaks["hbm_gbs"], "us_per_launch": ms_step / L * 1e3, "algorithmic_bytes_per_launch": layer_bytes,
-                               "distinct_experts_per_layer": distinct, "traffic": recorded_traffic(f"{'window_kernel' if one_launch else 'layer_three_launches'}_rows{rows}"),
+                               "distinct_experts_per_layer": distinct, "traffic": recorded_traffic(f"window_kernel_rows{rows}"),
                                "instruction_ceiling_gbs": INSTRUCTION_CEILING_GBS, "frac_of_instruction_ceiling": gbs / INSTRUCTION_CEILING_GBS}
+        elif G == 1:
+            # the dominant kernel alone: the gate/up GEMV (with grouping, input rotation and the SwiGLU epilogue inside), every
+            # layer back to back
+            m = epm.owner(0)
+            m.set_phases(4)                                          # gate/up only (scratch of the last step stays in place)
+
+            def gateup_pass():
+                for l in range(L):
+                    m.run(self.structs[l], x_d[l], p_d[l], w_d[l], rows)
+            gg = self.graph_of(gateup_pass)
+            ms_pass = self.timed((lambda: gg.replay()) if gg is not None else gateup_pass, max(5, steps), 3)
+            m.set_phases(31)
+            gu_bytes = distinct * GATEUP_BYTES_E + rows * H * 2 * 2
+            gbs = gu_bytes / (ms_pass / L * 1e-3) / 1e9
+            lgbs = layer_bytes / (ms_step / L * 1e-3) / 1e9
+            res["roofline"] = {"bound": "hbm", "kernel": "gemv_kernel<2,*> (gate/up grouped GEMV + grouping + input rotation + SwiGLU epilogue)",
+                               "achieved": gbs, "peak": self.peaks["hbm_gbs"], "peak_source": self.peaks["source"] + " hbm_gbs", "unit": "GB/s",
+                               "frac": gbs / self.peaks["hbm_gbs"], "us_per_launch": ms_pass / L * 1e3, "algorithmic_bytes_per_launch": gu_bytes,
+                               "distinct_experts_per_layer": distinct, "traffic": recorded_traffic(f"gemv_gateup_rows{rows}"),
+                               "instruction_ceiling_gbs": INSTRUCTION_CEILING_GBS, "frac_of_instruction_ceiling": gbs / INSTRUCTION_CEILING_GBS,
+                               "layer": {"algorithmic_bytes": layer_bytes, "us": ms_step / L * 1e3, "gbs": lgbs, "frac": lgbs / self.peaks["hbm_gbs"],
+                                         "frac_of_instruction_ceiling": lgbs / INSTRUCTION_CEILING_GBS}}
         else:
             res["distinct_experts_per_layer"] = distinct
             # per-phase split of one layer: this rank's share without the exchange, and with it

@@ -88,7 +88,89 @@ SYMBOLS = {
     "glmflash_ep_set_wait_limit": (_I, [_P, C.c_uint32]),
     "glmflash_ep_local_base": (_P, [_P]),
     "glmflash_ep_connect_ptrs": (_I, [_P, _P]),
+    "glmflash_prepared_open": (_I, [C.c_char_p, _P]),
+    "glmflash_prepared_close": (None, [_P]),
+    "glmflash_prepared_key_int": (_I, [_P, C.c_char_p, _P]),
+    "glmflash_prepared_tensor_count": (_I, [_P]),
+    "glmflash_prepared_tensor_name": (C.c_char_p, [_P, _I]),
+    "glmflash_prepared_tensor": (_I, [_P, C.c_char_p, _P]),
+    "glmflash_prepared_verify": (_I, [_P]),
+    "glmflash_prepared_load": (_I, [_P, _P, _I]),
+    "glmflash_expert_bank_from_tp": (_I, [_P, _I, C.c_char_p, _I, _I, _P, _P]),
+    "glmflash_expert_bank_weights": (_I, [_P, _P, _P, _P]),
+    "glmflash_expert_bank_free": (None, [_P]),
 }
+
+
+class TensorInfo(C.Structure):
+    _fields_ = [("dtype", C.c_char * 16), ("rank", C.c_int32), ("on_device", C.c_int32), ("contiguous", C.c_int32),
+                ("reserved", C.c_int32), ("shape", C.c_int64 * 8), ("stride", C.c_int64 * 8), ("nbytes", C.c_int64), ("ptr", C.c_void_p)]
+
+
+class Prepared:
+    """Prepared::{open, tensor, load_selected} + Loaded::pointer (reference src/prepared.rs:151-377).  Opening and
+    verifying need no GPU."""
+
+    def __init__(self, manifest_path):
+        self._h = C.c_void_p()
+        _check(lib().glmflash_prepared_open(str(manifest_path).encode(), C.byref(self._h)))
+
+    def key_int(self, name):
+        v = C.c_int64()
+        _check(lib().glmflash_prepared_key_int(self._h, name.encode(), C.byref(v)))
+        return v.value
+
+    def names(self):
+        L = lib()
+        return [L.glmflash_prepared_tensor_name(self._h, i).decode() for i in range(L.glmflash_prepared_tensor_count(self._h))]
+
+    def tensor(self, name):
+        info = TensorInfo()
+        _check(lib().glmflash_prepared_tensor(self._h, name.encode(), C.byref(info)))
+        return {"dtype": info.dtype.decode(), "shape": list(info.shape[: info.rank]), "stride": list(info.stride[: info.rank]),
+                "nbytes": info.nbytes, "on_device": bool(info.on_device), "contiguous": bool(info.contiguous), "ptr": info.ptr}
+
+    def verify(self):
+        _check(lib().glmflash_prepared_verify(self._h))
+
+    def load(self, prefixes=()):
+        arr = (C.c_char_p * max(1, len(prefixes)))(*[p.encode() for p in prefixes])
+        _check(lib().glmflash_prepared_load(self._h, arr, len(prefixes)))
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            lib().glmflash_prepared_close(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+
+class ExpertBank:
+    """Whole experts [e_lo, e_hi) assembled from the tensor-parallel shards of `stem` (glmflash_expert_bank_from_tp)."""
+
+    def __init__(self, shards, stem, e_lo, e_hi, stream=None):
+        arr = (C.c_void_p * len(shards))(*[s._h for s in shards])
+        self._h = C.c_void_p()
+        _check(lib().glmflash_expert_bank_from_tp(arr, len(shards), stem.encode(), e_lo, e_hi, _stream_ptr(stream), C.byref(self._h)))
+        self.weights = Weights()
+        h, i = C.c_int32(), C.c_int32()
+        _check(lib().glmflash_expert_bank_weights(self._h, C.byref(self.weights), C.byref(h), C.byref(i)))
+        self.hidden, self.inter = h.value, i.value
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            lib().glmflash_expert_bank_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 _lib = None
 

@@ -259,6 +259,49 @@ int glmflash_topk(void *stream, const float *logits, int rows, int experts, int 
 int glmflash_route(void *stream, const uint16_t *x, int x_stride, const uint16_t *wr, int rows, int hidden, int experts,
                    int topk, float *logits, int32_t *picks, float *weights, int pdl);
 
+/* ---- prepared weights  (src/prepared.rs:15-377; layout: docs/ARTIFACTS.md "Prepared target") ---------------------
+ * A prepared model is a JSON manifest (format 1: file size, chunk size, one SHA-256 per chunk, storage table, object
+ * tree with tensor leaves, preparation key) next to its payload `data.bin`.  open parses and validates the manifest
+ * (Prepared::open_parts: chunk bound 128 MiB, hash count, payload size, ordered storages inside the payload, every
+ * tensor inside its storage and on its storage's device); it needs no GPU.  Tensor paths are upstream's:
+ * `weights.layers[3].moe.experts.gt` (fields '.', sequences '[i]', dict keys '[key]').  The model-specific checks of
+ * Prepared::open (model name, rank / world, geometry) are the host's: glmflash_prepared_key_int reads the key. */
+typedef struct glmflash_prepared glmflash_prepared;
+typedef struct glmflash_tensor_info {
+    char    dtype[16];     /* "int32", "float16", ... (src/prepared.rs:42-50)                                  */
+    int32_t rank;          /* at most 8                                                                        */
+    int32_t on_device;     /* 1: the tensor's storage is a CUDA storage                                        */
+    int32_t contiguous;    /* 1: dense row-major strides (Prepared::expect)                                    */
+    int32_t reserved;
+    int64_t shape[8], stride[8];   /* elements                                                                 */
+    int64_t nbytes;        /* from the first to the end of the last element                                    */
+    void   *ptr;           /* after glmflash_prepared_load: device (or host, for cpu storages) address; else NULL */
+} glmflash_tensor_info;
+int  glmflash_prepared_open(const char *manifest_path, glmflash_prepared **out);
+void glmflash_prepared_close(glmflash_prepared *p);
+int  glmflash_prepared_key_int(const glmflash_prepared *p, const char *name, int64_t *value);
+int  glmflash_prepared_tensor_count(const glmflash_prepared *p);
+const char *glmflash_prepared_tensor_name(const glmflash_prepared *p, int i);          /* sorted paths */
+int  glmflash_prepared_tensor(const glmflash_prepared *p, const char *name, glmflash_tensor_info *info);   /* Loaded::pointer */
+/* Reads the whole payload and checks every chunk against its SHA-256 (no GPU). */
+int  glmflash_prepared_verify(glmflash_prepared *p);
+/* Prepared::load_selected: uploads the storages that hold a tensor whose path starts with one of the prefixes (all of
+ * them when n_prefixes == 0); every chunk that is read is verified first.  Allocates and synchronises: a set-up call. */
+int  glmflash_prepared_load(glmflash_prepared *p, const char *const *prefixes, int n_prefixes);
+
+/* Upstream shards every expert four ways by tensor parallelism: a rank's `...moe.experts.{gt,ut}` hold 512 of the
+ * intermediate's columns, `dt` the matching 512 rows, `suh_d / svh_g / svh_u` the matching slices (src/experts.rs:146-156).
+ * This puts the slices of the experts [e_lo, e_hi) back together (device copies on `stream`), so that an expert-parallel
+ * rank owns whole experts.  shards: the n_shards ranks' manifests in rank order, the tensors under `stem` loaded on the
+ * current device.  glmflash_expert_bank_weights gives the nine pointers in the form the owners take (indexed by the
+ * GLOBAL expert id: only ids of the window may be touched -- configure expert_lo / expert_hi accordingly, and
+ * shared_exl3 = 0: upstream's shared expert is not an EXL3 expert) and the re-assembled sizes. */
+typedef struct glmflash_expert_bank glmflash_expert_bank;
+int  glmflash_expert_bank_from_tp(glmflash_prepared *const *shards, int n_shards, const char *stem, int e_lo, int e_hi, void *stream,
+                                  glmflash_expert_bank **out);
+int  glmflash_expert_bank_weights(const glmflash_expert_bank *b, glmflash_weights *w, int32_t *hidden, int32_t *inter);
+void glmflash_expert_bank_free(glmflash_expert_bank *b);
+
 #ifdef __cplusplus
 }
 #endif

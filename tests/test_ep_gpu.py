@@ -34,7 +34,9 @@ def _worker(rank, world, port, rows_list, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         res = []
-        for rows in rows_list:
+        for rows, launches in [(r, k) for r in rows_list for k in ((3, 1) if r <= 16 else (3,))]:
+            # launches = 1: the one-launch layer kernel with the exchange inside; 3: expert kernels, then the exchange kernel
+            os.environ["GLMFLASH_LAYER_KERNELS"] = str(launches)
             layer = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nvlink")
             base = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nccl")
             single = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows))
@@ -50,6 +52,7 @@ def _worker(rank, world, port, rows_list, q):
                 single.run(bank, x, pd, wd, rows)
                 torch.cuda.synchronize()
                 assert int(layer.ep.status.cpu()[0]) == 0, "a bounded peer wait gave up"
+                layer.check()
                 assert torch.equal(out, again) and torch.equal(out, nccl), "fused NVLink exchange != NCCL all-gather + ordered sum"
                 ref = single.output[:rows].clone()
                 chk = [torch.empty_like(out) for _ in range(world)]
