@@ -99,7 +99,90 @@ SYMBOLS = {
     "glmflash_expert_bank_from_tp": (_I, [_P, _I, C.c_char_p, _I, _I, _P, _P]),
     "glmflash_expert_bank_weights": (_I, [_P, _P, _P, _P]),
     "glmflash_expert_bank_free": (None, [_P]),
+    "glmflash_graph_policy_default": (_I, [_I, _P]),
+    "glmflash_graph_cache_new": (_I, [_P, _P]),
+    "glmflash_graph_cache_free": (None, [_P]),
+    "glmflash_graph_cache_action": (_I, [_P, C.c_uint64]),
+    "glmflash_graph_cache_insert": (_I, [_P, C.c_uint64, C.c_uint64, _P]),
+    "glmflash_graph_cache_get": (_P, [_P, C.c_uint64]),
+    "glmflash_graph_cache_stats": (_I, [_P, _P]),
+    "glmflash_graph_cache_run": (_I, [_P, C.c_uint64, _P, _P, _P]),
 }
+
+
+class GraphPolicy(C.Structure):
+    _fields_ = [("bounded", C.c_int32), ("entries", C.c_uint32), ("nodes", C.c_uint64), ("sightings", C.c_uint32), ("after", C.c_uint32)]
+
+
+class GraphStats(C.Structure):
+    _fields_ = [(n, C.c_uint64) for n in ("hits", "eager", "captures", "evictions", "oversized", "retained_graphs", "retained_nodes",
+                                          "peak_graphs", "peak_nodes", "largest_graph_nodes", "tracked_sightings")]
+
+
+ENQUEUE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p)
+REPLAY, EAGER, CAPTURE = 0, 1, 2
+
+
+class GraphCache:
+    """Cache::{action, insert} of the reference's verify-window graph cache (src/verifier_graph_cache.rs) and the capture /
+    replay step built on it.  The policy part needs no GPU."""
+
+    def __init__(self, policy=None, bounded=True):
+        if policy is None:
+            policy = GraphPolicy()
+            _check(lib().glmflash_graph_policy_default(int(bounded), C.byref(policy)))
+        self.policy = policy
+        self._h = C.c_void_p()
+        _check(lib().glmflash_graph_cache_new(C.byref(policy), C.byref(self._h)))
+        self._keep = []
+
+    def action(self, key):
+        return lib().glmflash_graph_cache_action(self._h, key)
+
+    def insert(self, key, nodes, graph_exec=None):
+        return lib().glmflash_graph_cache_insert(self._h, key, nodes, graph_exec)
+
+    def contains(self, key):
+        return bool(lib().glmflash_graph_cache_get(self._h, key)) or key in self._null_keys()
+
+    def _null_keys(self):
+        return ()
+
+    def stats(self):
+        st = GraphStats()
+        _check(lib().glmflash_graph_cache_stats(self._h, C.byref(st)))
+        return {n: getattr(st, n) for n, _ in GraphStats._fields_}
+
+    def run(self, key, fn, stream=None):
+        """fn(): enqueue the window's work on the current torch stream (it is made current for the call)."""
+        torch = _torch()
+        st = stream if stream is not None else torch.cuda.current_stream()
+        err = []
+
+        def tramp(_user, _stream):
+            try:
+                with torch.cuda.stream(st):
+                    fn()
+                return 0
+            except Exception as ex:          # noqa: BLE001 -- nothing may cross the C boundary
+                err.append(ex)
+                return -1
+        cb = ENQUEUE_FN(tramp)
+        rc = lib().glmflash_graph_cache_run(self._h, key, C.c_void_p(st.cuda_stream), cb, None)
+        if err:
+            raise err[0]
+        _check(rc)
+
+    def close(self):
+        if getattr(self, "_h", None) and self._h.value:
+            lib().glmflash_graph_cache_free(self._h)
+            self._h = C.c_void_p()
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
 
 
 class TensorInfo(C.Structure):

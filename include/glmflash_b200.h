@@ -302,6 +302,38 @@ int  glmflash_expert_bank_from_tp(glmflash_prepared *const *shards, int n_shards
 int  glmflash_expert_bank_weights(const glmflash_expert_bank *b, glmflash_weights *w, int32_t *hidden, int32_t *inter);
 void glmflash_expert_bank_free(glmflash_expert_bank *b);
 
+/* ---- verify-window graph cache  (src/verifier_graph_cache.rs; used by src/multi_decode.rs:470-537) ----------------
+ * Upstream captures one CUDA graph per (slot, parity, rows, geometry) of its speculative-verify windows -- two to four
+ * requests share one <= 16-row expert call -- and keeps them under two caps.  The same policy: action() says replay,
+ * run eagerly (a bounded cache captures a key only from its `after`-th sighting on) or capture; insert() retains a
+ * captured graph, evicting least recently used entries while there are `entries` of them or more than `nodes` graph
+ * nodes; a graph that alone exceeds `nodes` is handed back.  The unbounded policy clears everything when it is full.
+ * key: any 64-bit value the host derives from the window's shape, e.g. rows | parity << 8 | slot << 16. */
+typedef struct glmflash_graph_policy {
+    int32_t  bounded;      /* 1: upstream's ALASKA_VERIFY_GRAPH_CACHE=1 policy, 0: its default                  */
+    uint32_t entries;      /* graphs retained at most                                                          */
+    uint64_t nodes;        /* graph nodes retained at most (bounded)                                           */
+    uint32_t sightings;    /* keys tracked before their capture (bounded)                                      */
+    uint32_t after;        /* capture at the after-th sighting of a key                                        */
+} glmflash_graph_policy;
+typedef struct glmflash_graph_stats {
+    uint64_t hits, eager, captures, evictions, oversized, retained_graphs, retained_nodes, peak_graphs, peak_nodes,
+             largest_graph_nodes, tracked_sightings;
+} glmflash_graph_stats;
+enum { GLMFLASH_GRAPH_REPLAY = 0, GLMFLASH_GRAPH_EAGER = 1, GLMFLASH_GRAPH_CAPTURE = 2 };
+typedef struct glmflash_graph_cache glmflash_graph_cache;
+typedef int (*glmflash_enqueue_fn)(void *user, void *stream);
+int   glmflash_graph_policy_default(int bounded, glmflash_graph_policy *out);
+int   glmflash_graph_cache_new(const glmflash_graph_policy *policy, glmflash_graph_cache **out);
+void  glmflash_graph_cache_free(glmflash_graph_cache *c);
+int   glmflash_graph_cache_action(glmflash_graph_cache *c, uint64_t key);                 /* GLMFLASH_GRAPH_* or -1 */
+int   glmflash_graph_cache_insert(glmflash_graph_cache *c, uint64_t key, uint64_t nodes, void *graph_exec);
+void *glmflash_graph_cache_get(const glmflash_graph_cache *c, uint64_t key);              /* cudaGraphExec_t or NULL */
+int   glmflash_graph_cache_stats(const glmflash_graph_cache *c, glmflash_graph_stats *out);
+/* One window: replay, run eagerly or capture + launch + retain, as the policy decides.  `enqueue` puts the window's
+ * work on the stream it is given (any sequence of this library's run calls qualifies) and returns 0 or -1. */
+int   glmflash_graph_cache_run(glmflash_graph_cache *c, uint64_t key, void *stream, glmflash_enqueue_fn enqueue, void *user);
+
 #ifdef __cplusplus
 }
 #endif
