@@ -50,12 +50,50 @@ def computed_here(picks, rank, world, experts, layer, max_rows=None):
     return routed | shared
 
 
-def exchange(partial, gathered, out, group=None, rank_sum=None):
+class ExchangeError(RuntimeError):
+    """A rank did not take part in an exchange (it failed, or never arrived), or the collective itself failed."""
+
+
+def arrive(store, step, rank, world, timeout_s=5.0):
+    """Host-side agreement before exchange `step`: no rank enters the collective unless every rank has arrived (the
+    reference agrees across ranks before its first exchange, src/roce.rs:235-273, and closes a failed transfer group
+    instead of leaving peers inside it, src/nccl_exchange_plan.rs:163-197).  `store`: a torch.distributed store.  A rank
+    that cannot take part calls withdraw(); its peers then raise ExchangeError at once, and after `timeout_s` when a
+    rank simply never arrives -- nobody is left hanging inside a collective."""
+    import datetime
+    import time
+    store.set(f"ep/{step}/{rank}", b"ok")
+    deadline = time.monotonic() + timeout_s
+    for k in range(world):
+        left = max(0.05, deadline - time.monotonic())
+        try:
+            store.wait([f"ep/{step}/{k}"], datetime.timedelta(seconds=left))
+        except Exception as ex:                                # the store's time-out
+            raise ExchangeError(f"rank {k} did not reach exchange {step} within {timeout_s} s") from ex
+        word = bytes(store.get(f"ep/{step}/{k}"))
+        if word != b"ok":
+            raise ExchangeError(f"rank {k} withdrew from exchange {step}: {word.decode(errors='replace')}")
+
+
+def withdraw(store, step, rank, why):
+    """Tell the peers that this rank will not take part in exchange `step` (see arrive)."""
+    store.set(f"ep/{step}/{rank}", ("failed: " + str(why)).encode())
+
+
+def exchange(partial, gathered, out, group=None, rank_sum=None, all_gather=None):
     """All-gather `partial` [rows][H] fp32 into `gathered` [world][rows][H] and add the ranks' rows in ascending
-    rank order into `out`.  `rank_sum(gathered, out)` is the device kernel (glmflash_rank_sum) on GPUs; on CPU
+    rank order into `out`.  A failing collective surfaces as ExchangeError.  `rank_sum(gathered, out)` is the device kernel (glmflash_rank_sum) on GPUs; on CPU
     ranks the same ordered sum is done with torch."""
     import torch.distributed as dist
-    dist.all_gather_into_tensor(gathered.view(-1), partial.reshape(-1), group=group)
+    try:
+        if all_gather is not None:                             # injectable, as the reference's plan takes its NCCL calls as closures
+            all_gather(gathered.view(-1), partial.reshape(-1))
+        else:
+            dist.all_gather_into_tensor(gathered.view(-1), partial.reshape(-1), group=group)
+    except ExchangeError:
+        raise
+    except Exception as ex:
+        raise ExchangeError(f"all-gather of the partial layer outputs failed: {ex}") from ex
     if rank_sum is not None:
         rank_sum(gathered, out)
     else:

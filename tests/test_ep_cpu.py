@@ -87,3 +87,77 @@ def test_windows(pkg):
         ep.expert_window(0, 3, 64)
     with pytest.raises(ValueError):
         ep.expert_window(2, 2, 64)
+
+
+def _failing_worker(rank, world, port, store_port, mode, q):
+    """mode 'absent': rank 1 raises before exchange 2 and says nothing; 'withdraw': it tells the peers; 'collective': its
+    all-gather closure reports an error code.  Nobody may hang: every rank ends with a result or an ExchangeError."""
+    sys.path.insert(0, ROOT)
+    import datetime
+    import time
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as entry
+    entry.load_package()
+    from glmflash_b200 import ep
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=20))
+    store = dist.TCPStore("127.0.0.1", store_port, world, rank == 0, timeout=datetime.timedelta(seconds=20))
+    log = []
+    try:
+        for step in range(4):
+            part = torch.full((3, 8), float(rank + 1 + step))
+            gathered, out = torch.empty((world, 3, 8)), torch.empty((3, 8))
+            t0 = time.monotonic()
+            try:
+                if rank == 1 and step == 2 and mode in ("absent", "withdraw"):
+                    if mode == "withdraw":
+                        ep.withdraw(store, step, rank, "device status word 4")
+                    raise RuntimeError("rank 1 lost its GPU work before the exchange")
+                ep.arrive(store, step, rank, world, timeout_s=2.0)
+                inject = None
+                if mode == "collective" and step == 2:
+                    def inject(dst, src):
+                        raise RuntimeError("ncclSystemError (2)")
+                ep.exchange(part, gathered, out, all_gather=inject)
+                log.append((step, "ok", float(out[0, 0])))
+            except ep.ExchangeError as ex:
+                log.append((step, "exchange-error", str(ex), time.monotonic() - t0))
+                break
+            except RuntimeError as ex:
+                log.append((step, "local-failure", str(ex)))
+                break
+        q.put((rank, log))
+        q.close()
+        q.join_thread()
+    finally:
+        os._exit(0)                      # a rank that failed leaves without a collective tear-down
+
+
+@pytest.mark.parametrize("mode", ["absent", "withdraw", "collective"])
+def test_a_failing_rank_gives_its_peers_an_error_not_a_hang(mode):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port, store_port = _free_port(), _free_port()
+    procs = [ctx.Process(target=_failing_worker, args=(r, 2, port, store_port, mode, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=60) for _ in range(2))
+    for p in procs:
+        p.join(timeout=30)
+    want_sum = lambda step: float(1 + step) + float(2 + step)
+    for rank in (0, 1):
+        assert [e[:2] for e in res[rank][:2]] == [(0, "ok"), (1, "ok")]
+        assert res[rank][0][2] == want_sum(0) and res[rank][1][2] == want_sum(1)
+    if mode == "collective":
+        for rank in (0, 1):
+            assert res[rank][2][1] == "exchange-error" and "all-gather" in res[rank][2][2] and "ncclSystemError" in res[rank][2][2]
+    else:
+        assert res[1][2][1] == "local-failure"
+        step, kind, msg, waited = res[0][2]
+        assert kind == "exchange-error" and "rank 1" in msg
+        if mode == "withdraw":
+            assert "withdrew" in msg and "status word 4" in msg and waited < 1.5      # told at once, not after the time-out
+        else:
+            assert "did not reach exchange 2" in msg and waited < 10

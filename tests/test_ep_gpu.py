@@ -120,6 +120,20 @@ def test_peer_that_never_arrives_times_out(pkg, synth, cuda):
     assert torch.allclose(eps[0].output[:rows], want, rtol=1e-5, atol=1e-5)
 
 
+def test_connect_rejects_a_peer_built_with_another_configuration(pkg, cuda):
+    """The handle blob carries a hash of the exchange's layout; a rank whose hidden size, row limit or world differs is
+    named at connect time, before any peer memory is mapped, instead of being indexed with the wrong strides."""
+    import ctypes
+    from glmflash_b200 import lib
+    mk = lambda **kw: pkg.make_config(H, I, E, S, shared_exl3=0, expert_lo=32, expert_hi=64, pdl=0, **kw)
+    for other in (mk(max_rows=8), pkg.make_config(H // 2, I, E, S, max_rows=4, shared_exl3=0, expert_lo=32, expert_hi=64, pdl=0)):
+        peer = pkg.EpCombine(other, 1, 2, None)
+        blob = ctypes.create_string_buffer(lib().glmflash_ep_handle_bytes())
+        assert lib().glmflash_ep_get_handle(peer._h, blob) == 0
+        with pytest.raises(RuntimeError, match="rank 1 was built with a different configuration"):
+            pkg.EpCombine(mk(max_rows=4), 0, 2, lambda mine: [mine, bytes(blob.raw)])
+
+
 def C_void(t):
     import ctypes
     return ctypes.c_void_p(t.data_ptr())

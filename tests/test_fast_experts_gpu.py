@@ -21,12 +21,22 @@ def _bf16_dev(x_bits, cuda):
 
 @pytest.fixture(scope="module")
 def bank(synth):
-    return synth.expert_bank(1001, H, I, E, svh_scale=True)
+    return synth.expert_bank(1001, H, I, E, svh_scale=True)      # unit-variance pre-activations: nothing saturates
 
 
 @pytest.fixture(scope="module")
 def dbank(bank, synth, cuda):
     return synth.to_device(bank, cuda)
+
+
+@pytest.fixture(scope="module")
+def bank_bench(synth):
+    return synth.expert_bank(1000, H, I, E)                      # the benchmark's distribution (SwiGLU mostly clamped)
+
+
+@pytest.fixture(scope="module")
+def dbank_bench(bank_bench, synth, cuda):
+    return synth.to_device(bank_bench, cuda)
 
 
 def probe_picks(rows, spread=16):
@@ -48,8 +58,13 @@ def run_fast(pkg, oracle, cuda, wd, x_bits, picks, rows, max_rows, shared_x=Fals
     return fe.output[: rows * S].cpu().numpy().copy(), fe, args
 
 
-@pytest.mark.parametrize("rows,max_rows", [(1, 129), (63, 129), (64, 129), (65, 129), (129, 129), (300, 512)])
-def test_fast_vs_oracle(pkg, oracle, synth, cuda, bank, dbank, rows, max_rows):
+# the reference probe's row counts and member strides (src/fast_experts.rs:247-254), a mid-size chunk, and the owner's
+# largest capacity (src/fast_experts.rs:44-47), on both scale distributions
+@pytest.mark.parametrize("which", ["scaled", "benchmark"])
+@pytest.mark.parametrize("rows,max_rows", [(1, 129), (63, 129), (64, 129), (65, 129), (129, 129), (300, 512), (4097, 4097), (500, 8192)])
+def test_fast_vs_oracle(pkg, oracle, synth, cuda, bank, dbank, bank_bench, dbank_bench, rows, max_rows, which):
+    if which == "benchmark":
+        bank, dbank = bank_bench, dbank_bench
     x = synth.activations_bf16(100 + rows, rows, H)
     picks = probe_picks(rows)
     y, fe, _ = run_fast(pkg, oracle, cuda, dbank, x, picks, rows, max_rows)
@@ -130,9 +145,12 @@ def test_fast_row_independence_and_replay(pkg, oracle, synth, cuda, dbank):
         assert (fe.output[: rows * S].cpu().numpy().view(np.uint32) == full.view(np.uint32)).all()
 
 
-def test_prefill_config4_vs_upstream(pkg, oracle, synth, cuda, bank, dbank):
+@pytest.mark.parametrize("which", ["scaled", "benchmark"])
+def test_prefill_config4_vs_upstream(pkg, oracle, synth, cuda, bank, dbank, bank_bench, dbank_bench, which):
     """Benchmark config 4: 4096 tokens, uniform random top-4 routing (about 256 tokens per expert)."""
     import torch
+    if which == "benchmark":
+        bank, dbank = bank_bench, dbank_bench
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import ref_gpu
     rows = 4096
