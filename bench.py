@@ -81,6 +81,40 @@ def recorded_traffic(key):
     return float(rec["traffic_bytes"])
 
 
+TRAFFIC_SOURCES = {"gemv": "glm-flash-rs_b200/csrc/gemv.cuh", "window": "glm-flash-rs_b200/csrc/window.cu",
+                   "fast": "glm-flash-rs_b200/csrc/fast_experts.cu"}
+
+
+def record_traffic(csv_path, key, kernel_regex, command):
+    """Summary step of an ncu capture: read the `--csv` log of a run that collected dram__bytes_read.sum and
+    dram__bytes_write.sum, average read + write per launch over the kernels whose name matches, and store the figure in
+    profiles/traffic.json under `key`, with the hash of the kernel source it was measured on and the capture's command.
+    recorded_traffic() hands the figure to the roofline only while that source is unchanged."""
+    import csv
+    import re
+    scale = {"byte": 1.0, "Kbyte": 1e3, "Mbyte": 1e6, "Gbyte": 1e9, "Tbyte": 1e12}
+    lines = [ln for ln in open(csv_path, newline="") if ln.startswith('"')]
+    rows = list(csv.DictReader(lines))
+    per = {}
+    for r in rows:
+        if r.get("Metric Name") in ("dram__bytes_read.sum", "dram__bytes_write.sum") and re.search(kernel_regex, r["Kernel Name"]):
+            v = float(r["Metric Value"].replace(",", "")) * scale[r["Metric Unit"]]
+            per.setdefault(r["ID"], {})[r["Metric Name"]] = v
+    full = [d for d in per.values() if len(d) == 2]
+    if not full:
+        sys.exit(f"no launch of /{kernel_regex}/ with both DRAM counters in {csv_path}")
+    rd = sum(d["dram__bytes_read.sum"] for d in full) / len(full)
+    wr = sum(d["dram__bytes_write.sum"] for d in full) / len(full)
+    source = TRAFFIC_SOURCES[key.split("_")[0]]
+    out = os.path.join(ROOT, "profiles", "traffic.json")
+    table = json.load(open(out)) if os.path.exists(out) else {}
+    table[key] = {"traffic_bytes": round(rd + wr), "dram_read_bytes": round(rd), "dram_write_bytes": round(wr), "launches": len(full),
+                  "kernel": kernel_regex, "source": source,
+                  "source_sha256": hashlib.sha256(open(os.path.join(ROOT, source), "rb").read()).hexdigest(), "command": command}
+    json.dump(table, open(out, "w"), indent=1, sort_keys=True)
+    print(json.dumps({key: table[key]}))
+
+
 class ClockSampler:
     """nvidia-smi clock / throttle samples while the timed regions run."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
@@ -550,7 +584,12 @@ def main():
     ap.add_argument("--layer-kernels", type=int, default=3, choices=[1, 3],
                     help="windows of <= 16 rows: 3 = gate/up, down, combine (default); 1 = the one-launch layer kernel (comparison runs)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--record-traffic", nargs=4, metavar=("NCU_CSV", "KEY", "KERNEL_REGEX", "COMMAND"),
+                    help="no benchmark: store the per-launch DRAM traffic of an ncu --csv log in profiles/traffic.json (needs no GPU)")
     args = ap.parse_args()
+    if args.record_traffic:
+        record_traffic(*args.record_traffic)
+        return
     args.warmup = max(args.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

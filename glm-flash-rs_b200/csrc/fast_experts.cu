@@ -473,13 +473,17 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
         const int m = q * 32 + lane, em = tl * 128 + m;      // row of the tile, row of the item (0..255)
         uint32_t pc = 0;
         bool ok = true;
-        for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        // A warp whose wait gave up (or that sees the abort flag) does not leave this loop: it walks the remaining items
+        // arriving at the two barriers only, so that a sibling which passed the same wait at the last moment never
+        // stands alone at a barrier of eight warps.
+        for (int item = blockIdx.x; item < total; item += gridDim.x) {
             const ItemInfo t = item_info(item, NB, pairs_all, pair_base, single_base, row_base, a.ids);
             const bool has = tl < t.ntiles;
             const int cnt = tl == 0 ? t.cnt0 : t.cnt1;
             // scale vectors of (expert, column block): written by the first 128 epilogue threads, read by all 256
             asm volatile("bar.sync 1, 256;");
-            if (em < 128) {
+            if (ok && *abort_flag) ok = false;
+            if (ok && em < 128) {
                 const size_t o = (size_t)t.e * a.N + t.nb * 128 + em;
                 // the 1 / sqrt(128) of every Hadamard transform is folded into the scale vectors here (the transform is
                 // linear), which takes one multiply per element out of each epilogue step
@@ -487,6 +491,7 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                 if (MATS == 2) { scales[128 + em] = __half2float(a.sv1[o]) * HAD_SCALE; scales[256 + em] = __half2float(a.sd[o]) * HAD_SCALE; }
             }
             asm volatile("bar.sync 1, 256;");
+            if (!ok) continue;
             float v[128];
             for (int pm = 0; pm < MATS; ++pm, ++pc) {
                 const uint32_t pb = pc & 1;

@@ -195,6 +195,24 @@ int  glmflash_moe_run_host(glmflash_moe *m, void *stream, const glmflash_weights
                            int x_stride, const int32_t *picks_host, const float *route_w_host, int rows,
                            float *out_host);
 
+/* PDL contract (config.pdl = 1): how a host kernel joins the chain at either edge of a layer, as upstream chains its own
+ * kernels around the expert loads (native/expert_loads.cu:38-44, src/experts.rs:350-354).  The kernels of a window of
+ * <= 16 rows, and the grouping, router, combine and exchange kernels of every window, are launched with the
+ * programmatic-stream-serialization attribute and execute griddepcontrol.wait in every CTA that does work, so "the
+ * kernel before has completed" is transitive along the stream; the plan / rotation / GEMM kernels in the middle of a
+ * prefill layer are plain launches (fully ordered).
+ *   In front of a layer (the producer of `input`, `picks`, `route_w`): nothing is required.  The first kernel of
+ *     glmflash_moe_run / glmflash_moe_run_ep / glmflash_route touches no global memory before its griddepcontrol.wait, so
+ *     the producer may be a plain kernel, or call griddepcontrol.launch_dependents as early as it likes (the layer's CTAs
+ *     then become resident and set up their barriers while the producer drains).
+ *   Behind a layer (a consumer of glmflash_moe_output / glmflash_ep_output), when the consumer is itself launched with the
+ *     attribute: the layer's last kernel calls griddepcontrol.launch_dependents at its start, so the consumer's CTAs may
+ *     start while the layer's last kernel (with GLMFLASH_LAYER_KERNELS=1: the whole layer) is still running.  Before its own
+ *     griddepcontrol.wait the consumer may read its own weights and any buffer the layer does not write (a prefetch);
+ *     it must not read the layer's output, pair buffer or status word, and must not write `input`, `picks`, `route_w`
+ *     or the weights.  After the wait everything the layer wrote is visible.
+ *   A consumer launched without the attribute is ordered after the whole layer, as any kernel in the stream. */
+
 /* ---- expert-parallel combine over NVLink ------------------------------------------------------------ */
 /* One owner per rank (one process per GPU).  It replaces upstream's gather + ordered sum after the MoE layer
  * (src/model.rs:485-496; Nccl::all_gather_f32 src/comm.rs:261-285 / Roce::gather src/roce.rs:283-330) by ONE kernel
