@@ -547,6 +547,22 @@ class Bench:
                 res["cpu_baseline"] = {"value": n / dt, "unit": "layer-tokens/s", "cores": host_threads(), "kind": "port",
                                        "sample": f"{n} of the {rows} tokens of one chunk ({dt:.1f} s); every touched expert is unpacked once per slice"}
         else:
+            # per-phase split of one chunk: this rank's share with a local combine and no exchange; the whole call; and the
+            # exchange kernel alone (combine of this rank's pairs + NVLink push + ordered sum) on the pair buffer left in place
+            m = epm.owner(0)
+
+            def solo():
+                l = state["i"] % L
+                state["i"] += 1
+                m.run(self.structs[l], x_d[l], p_d[l], w_d[l], rows, stream=self.stream)
+            ms_solo = self.timed(solo, max(3, steps // 2), 3)
+            res["phases_us_per_layer"] = {"rank_share_with_local_combine": ms_solo * 1e3, "with_exchange": ms_step * 1e3}
+            if args.exchange == "nvlink":
+                def xonly():
+                    epm.ep.combine(m.pairs_ptr, p_d[0], w_d[0], rows, True, stream=self.stream)
+                ms_x = self.timed(xonly, max(3, steps // 2), 3)
+                res["phases_us_per_layer"]["exchange_kernel_alone"] = ms_x * 1e3
+                res["phases_us_per_layer"]["exchange_bytes_out_per_rank"] = int(2 * rows * H * 4 * (G - 1) / G)
             res["ep_check"] = self.ep_check(epm, range(L), x_d, p_d, w_d, rows, rows)
             self.check_status(epm, f"prefill rows={rows} after ep_check")
         return res

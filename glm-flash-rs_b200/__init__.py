@@ -86,6 +86,7 @@ SYMBOLS = {
     "glmflash_route": (_I, [_P, _P, _I, _P, _I, _I, _I, _I, _P, _P, _P, _I]),
     "glmflash_ep_status": (_P, [_P]),
     "glmflash_ep_set_wait_limit": (_I, [_P, C.c_uint32]),
+    "glmflash_ep_set_exchange_bf16": (_I, [_P, _I]),
     "glmflash_ep_local_base": (_P, [_P]),
     "glmflash_ep_connect_ptrs": (_I, [_P, _P]),
     "glmflash_prepared_open": (_I, [C.c_char_p, _P]),
@@ -592,6 +593,10 @@ class EpCombine:
 
     def clear_status(self, stream=None):
         _check(lib().glmflash_ep_clear_status(self._h, _stream_ptr(stream)))
+
+    def set_exchange_bf16(self, on):
+        """Windows of more than 16 rows: partial rows cross NVLink as bf16 (every rank must choose the same)."""
+        _check(lib().glmflash_ep_set_exchange_bf16(self._h, int(bool(on))))
 
     def set_wait_limit(self, polls):
         _check(lib().glmflash_ep_set_wait_limit(self._h, polls))

@@ -13,7 +13,8 @@
 // one owner rank (chunks of 8 rows, dealt out in contiguous runs); every rank stores its partial of the row only into the
 // OWNER's receive slot, the owner
 // adds the slots in rank order and stores the finished row into every rank's result buffer, and every rank waits for
-// that.  Per rank about 2 x rows x H x 4 bytes cross NVLink instead of world x that (268 MB at 4096 rows on 8 GPUs).
+// that.  Per rank about 2 x rows x H x 4 bytes cross NVLink instead of world x that (268 MB at 4096 rows on 8 GPUs);
+// with glmflash_ep_set_exchange_bf16 the first of the two steps moves bf16 (1.5 x rows x H x 4 bytes in all).
 // Receive buffers are double-buffered by epoch parity; the epoch lives in device memory and is advanced by the
 // last CTA of a call, so captured graphs replay correctly.  A wait that gives up sets the status word (the
 // analogue of upstream's poison word, native/roce.cu:127-141) and the kernel returns; nothing spins unbounded.
@@ -137,7 +138,19 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
 // chunk has one owner rank (the owners' row ranges are multiples of EP_RB), so one fence and one flag per chunk and step
 // replace one per row.  A CTA only ever waits for the CTAs of the SAME chunk on other ranks, and every rank walks the
 // chunks in the same order, so no wait depends on a CTA that is dispatched later on its own GPU.
+// BF16: the partials of step 1 cross NVLink as bf16 (upstream casts every rank's rows to bf16 before its gather and adds
+// them in fp32, src/batch.rs:651-658); every rank's partial, the owner's own included, takes the same rounding, so the
+// sum still depends on nothing but the rank order.  The finished rows of step 2 stay fp32.
 constexpr int EP_RB = 8;
+__device__ __forceinline__ uint2 ep_pack_bf16(const float4 v) {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
+}
+__device__ __forceinline__ float4 ep_unpack_bf16(const uint2 w) {
+    return make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u), __uint_as_float(w.y << 16),
+                       __uint_as_float(w.y & 0xffff0000u));
+}
+template <bool BF16>
 __global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
                                                                       const float *__restrict__ route_w, float *__restrict__ out,
                                                                       EpPeers peers, unsigned *epoch_ptr, unsigned *done_ptr,
@@ -159,7 +172,9 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const floa
     for (int i = threadIdx.x; i < items; i += EP_THREADS) {
         const int r = r0 + i / q4, d = (i % q4) * 4;
         const float4 acc = ep_partial(Y, picks, route_w, r, d, slots, H, E, shared_exl3, e_lo, e_hi, srow_lo, srow_hi);
-        *reinterpret_cast<float4 *>(peers.recv[owner] + ((size_t)par * world + rank) * slot_elems + (size_t)r * H + d) = acc;
+        float *slot = peers.recv[owner] + ((size_t)par * world + rank) * slot_elems;
+        if (BF16) *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(slot) + (size_t)r * H + d) = ep_pack_bf16(acc);
+        else *reinterpret_cast<float4 *>(slot + (size_t)r * H + d) = acc;
     }
     __threadfence_system();
     __syncthreads();
@@ -173,10 +188,16 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const floa
         if (ok_sh)
             for (int i = threadIdx.x; i < items; i += EP_THREADS) {
                 const size_t off = (size_t)(r0 + i / q4) * H + (i % q4) * 4;
-                const float *src = peers.recv[rank] + (size_t)par * world * slot_elems + off;
-                float4 sum = __ldcg(reinterpret_cast<const float4 *>(src));
+                const float *base = peers.recv[rank] + (size_t)par * world * slot_elems;
+                auto slot_value = [&](int k) {
+                    if (BF16)
+                        return ep_unpack_bf16(__ldcg(reinterpret_cast<const uint2 *>(
+                            reinterpret_cast<const __nv_bfloat16 *>(base + (size_t)k * slot_elems) + off)));
+                    return __ldcg(reinterpret_cast<const float4 *>(base + (size_t)k * slot_elems + off));
+                };
+                float4 sum = slot_value(0);
                 for (int k = 1; k < world; ++k) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(src + (size_t)k * slot_elems));
+                    const float4 v = slot_value(k);
                     sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
                 }
                 for (int k = 0; k < world; ++k)
@@ -220,6 +241,7 @@ struct glmflash_ep {
     bool connected = false;
     float *out = nullptr;
     unsigned wait_polls = 2000000u;               // about a second of polling before a wait gives up
+    bool bf16_rows = false;                       // windows of more than 16 rows: partials cross NVLink as bf16
 };
 
 // What a rank publishes: the IPC handle of its receive area and a hash of everything the peers' address arithmetic
@@ -326,13 +348,19 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
     unsigned *epoch = (unsigned *)(h->local + h->tail());
     const dim3 grid((unsigned)((c.hidden / 4 + EP_THREADS - 1) / EP_THREADS), (unsigned)rows);
     if (rows > 16 && h->world > 1)
-        return launch_k(ep_exchange_rows_kernel, dim3((unsigned)((rows + EP_RB - 1) / EP_RB)), dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w,
+        return launch_k(h->bf16_rows ? ep_exchange_rows_kernel<true> : ep_exchange_rows_kernel<false>, dim3((unsigned)((rows + EP_RB - 1) / EP_RB)), dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w,
                         h->out, peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas,
                         c.slots, c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi,
                         h->wait_polls);
     return launch_k(ep_combine_kernel, grid, dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w, h->out,
                     peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas, c.slots,
                     c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi, h->wait_polls);
+}
+
+extern "C" int glmflash_ep_set_exchange_bf16(glmflash_ep *h, int on) {
+    GF_REQUIRE(h != nullptr, "null argument");
+    h->bf16_rows = on != 0;
+    return 0;
 }
 
 extern "C" int glmflash_ep_set_wait_limit(glmflash_ep *h, uint32_t polls) {

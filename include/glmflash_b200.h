@@ -249,6 +249,11 @@ const int32_t *glmflash_ep_status(const glmflash_ep *h);
 /* A peer time-out leaves the status word set, and while it is set every later wait gives up at once (a dead peer costs
  * one time-out, not one per block).  Clear it, in stream order, once the host has dealt with the failure. */
 int  glmflash_ep_clear_status(glmflash_ep *h, void *stream);
+/* Windows of more than 16 rows: send the ranks' partial rows as bf16 instead of fp32 (upstream casts the rows to bf16
+ * before its prefill gather and adds them in fp32, src/batch.rs:651-658).  Every rank must choose the same.  Default 0:
+ * fp32, whose result has the bytes of an fp32 all-gather + rank-ordered sum.  With 1 every partial, the owner's own
+ * included, is rounded to bf16 once before the fp32 sum in rank order; the finished rows stay fp32. */
+int  glmflash_ep_set_exchange_bf16(glmflash_ep *h, int on);
 /* Number of polls after which a wait for a peer gives up (default 2,000,000, about a second). */
 int  glmflash_ep_set_wait_limit(glmflash_ep *h, uint32_t polls);
 /* For a host that drives several GPUs from ONE process (peer access enabled by the host): connect with the peers'

@@ -134,6 +134,57 @@ def test_connect_rejects_a_peer_built_with_another_configuration(pkg, cuda):
             pkg.EpCombine(mk(max_rows=4), 0, 2, lambda mine: [mine, bytes(blob.raw)])
 
 
+@pytest.mark.parametrize("bf16", [False, True])
+def test_two_step_exchange_of_a_large_window_on_one_gpu(pkg, synth, cuda, bf16):
+    """Windows of more than 16 rows: every chunk of 8 rows has an owner rank that adds the ranks' partials in rank order
+    and hands the finished rows to everybody.  Two owners on ONE GPU, connected by pointers, called one after the other
+    with short wait limits (nothing hangs): rank 1 delivers its partials and gives up waiting; rank 0 then finds them and
+    finishes the chunks it owns (rows 0..31 of 64).  fp32 mode: the bytes of the plain rank-ordered sum; bf16 mode: every
+    partial rounded to bf16 once, then the fp32 sum in rank order (the reference's prefill exchange, src/batch.rs:651-658)."""
+    import torch
+    rows = 64
+    cfgs = [pkg.make_config(H, I, E, S, max_rows=rows, shared_exl3=0, expert_lo=r * 32, expert_hi=(r + 1) * 32, pdl=0) for r in (0, 1)]
+    eps = [pkg.EpCombine(cfgs[r], r, 2, None) for r in (0, 1)]
+    bases = [e.local_base for e in eps]
+    for e in eps:
+        e.connect_ptrs(bases)
+        e.set_wait_limit(20000)
+        e.set_exchange_bf16(bf16)
+    picks, rw = synth.route(15, rows, E, S - 1, uniform=True)
+    pd, wd = torch.from_numpy(picks).to(cuda), torch.from_numpy(rw).to(cuda)
+    Y = torch.randn((rows * S, H), dtype=torch.float32, device=cuda)
+    for step in range(2):                                        # the receive buffers alternate with the epoch
+        eps[1].combine(C_void(Y), pd, wd, rows, False)
+        torch.cuda.synchronize()
+        assert int(eps[1].status.cpu()[0]) == 4                  # rank 1's own chunks never got rank 0's partials
+        eps[1].clear_status()
+        got = eps[0].combine(C_void(Y), pd, wd, rows, True).clone()
+        torch.cuda.synchronize()
+        assert int(eps[0].status.cpu()[0]) == 4                  # ... and rank 0 waited in vain for rank 1's finished chunks
+        eps[0].clear_status()
+        y = Y.view(rows, S, H)
+        parts = []
+        for r in (0, 1):
+            mine = ((pd >= r * 32) & (pd < (r + 1) * 32)).float()
+            mine[:, S - 1] = 0.0
+            part = torch.zeros((rows, H), dtype=torch.float32, device=cuda)
+            for s_ in range(S - 1):                              # ascending slots, as the kernel adds them
+                part += (mine[:, s_] * wd[:, s_])[:, None] * y[:, s_]
+            if r == 0:
+                part += y[:, S - 1]                              # the shared expert's pair, weight 1, on rank 0
+            parts.append(part.bfloat16().float() if bf16 else part)
+        want = parts[0] + parts[1]
+        diff = (got[:32] - want[:32]).abs()
+        if not bf16:
+            assert float(diff.max()) < 2e-6, step                # fused vs separate multiply-add: an fp32 ulp
+        else:
+            # an fp32 ulp in a partial can flip its bf16 rounding: a handful of elements differ by one bf16 step
+            assert float((diff > 2e-6).float().mean()) < 1e-3 and float(diff.max()) < 0.1, step
+        if bf16:
+            plain = ((y[:, :S - 1] * wd[:, :S - 1, None]).sum(1) + y[:, S - 1])
+            assert not torch.allclose(got[:32], plain[:32], rtol=0, atol=1e-4)       # the rounding really happened
+
+
 def C_void(t):
     import ctypes
     return ctypes.c_void_p(t.data_ptr())
