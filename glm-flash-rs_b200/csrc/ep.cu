@@ -9,6 +9,9 @@
 //               (source rank, CTA) carries the epoch;
 //   3. wait:    the same CTA spins (bounded) on its own GPU's flags until every source has delivered the epoch;
 //   4. sum:     the slots are added in ascending rank order -- the reference's determinism rule -- into out.
+// Windows of <= 16 rows send flag and data in ONE 8-byte word (ep_combine_ll_kernel: every fp32 travels as the pair
+// {value, epoch}, an aligned 8-byte store arrives whole, and the receiver polls the words themselves), which takes the
+// fence and the separate flag round trip out of the latency: the push costs one NVLink crossing.
 // Windows of more than 16 rows use a two-step form of the same kernel (ep_exchange_rows_kernel): every row has
 // one owner rank (chunks of 8 rows, dealt out in contiguous runs); every rank stores its partial of the row only into the
 // OWNER's receive slot, the owner
@@ -43,6 +46,7 @@ struct EpPeers {
     unsigned *flags[EP_MAX_WORLD];      // flags[k]: rank k's flags [2][world][max_ctas]
     float *fin[EP_MAX_WORLD];           // fin[k]: rank k's finished rows [2][max_rows][H]          (two-step form)
     unsigned *fin_flags[EP_MAX_WORLD];  // fin_flags[k]: rank k's [2][max_ctas]                     (two-step form)
+    uint2 *ll[EP_MAX_WORLD];            // ll[k]: rank k's {value, epoch} words [2][world][max_rows][H]  (<= 16 rows)
 };
 
 // This rank's partial of row r, columns d..d+3: its computed pairs of the row, weights applied, ascending slots.
@@ -121,6 +125,78 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
             sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
         }
         *reinterpret_cast<float4 *>(out + (size_t)r * H + d) = sum;
+    }
+    // the last CTA of the call advances the epoch (after every CTA has read it)
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned n = gridDim.x * gridDim.y;
+        if (atomicAdd(done_ptr, 1u) == n - 1u) {
+            *done_ptr = 0u;
+            __threadfence();
+            *epoch_ptr = epoch;
+        }
+    }
+}
+
+// Windows of <= 16 rows, flag-in-data form.  A thread owns four columns of a row: it stores its partial as four
+// {value, epoch} words into slot `rank` of every PEER (two 16-byte volatile stores each; an aligned 8-byte word is
+// never torn), then adds the slots in ascending rank order, taking its own partial from registers and polling the
+// peers' words in its own GPU's memory until both halves of each 16-byte load carry the epoch.  Epochs start at 1 and
+// the buffers start zeroed; a slot is rewritten two epochs later, after its reader has finished (the writer cannot
+// finish the epoch in between without the reader's data of that epoch).
+__device__ __forceinline__ void st_volatile_v4(uint2 *p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 ld_volatile_v4(const uint2 *p) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
+__global__ void __launch_bounds__(EP_THREADS) ep_combine_ll_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
+                                                                   const float *__restrict__ route_w, float *__restrict__ out,
+                                                                   EpPeers peers, unsigned *epoch_ptr, unsigned *done_ptr,
+                                                                   int *status, int rank, int world, int rows, int max_rows,
+                                                                   int slots, int H, int E, int shared_exl3, int e_lo, int e_hi,
+                                                                   unsigned wait_polls) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int r = blockIdx.y;
+    const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    const unsigned epoch = *epoch_ptr + 1u;                   // every CTA reads it before the last one advances it
+    const unsigned par = epoch & 1u;
+    const size_t slot_words = (size_t)max_rows * H;
+    if (d < H) {
+        const float4 acc = ep_partial(Y, picks, route_w, r, d, slots, H, E, shared_exl3, e_lo, e_hi, 0, 0);
+        const size_t at = (size_t)r * H + d;
+        for (int k = 0; k < world; ++k) {
+            if (k == rank) continue;
+            uint2 *dst = peers.ll[k] + ((size_t)par * world + rank) * slot_words + at;
+            st_volatile_v4(dst, __float_as_uint(acc.x), epoch, __float_as_uint(acc.y), epoch);
+            st_volatile_v4(dst + 2, __float_as_uint(acc.z), epoch, __float_as_uint(acc.w), epoch);
+        }
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        bool ok = true;
+        for (int k = 0; k < world && ok; ++k) {
+            float4 v = acc;
+            if (k != rank) {
+                const uint2 *src = peers.ll[rank] + ((size_t)par * world + k) * slot_words + at;
+                uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 2);
+                for (unsigned i = 0; lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch; ++i) {
+                    if (i >= wait_polls) { ok = false; break; }
+                    if ((i & 1023u) == 1023u) {
+                        if (*reinterpret_cast<volatile int *>(status) == GF_STATUS_PEER_TIMEOUT) { ok = false; break; }
+                        __nanosleep(200);
+                    }
+                    lo = ld_volatile_v4(src);
+                    hi = ld_volatile_v4(src + 2);
+                }
+                v = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+            }
+            if (k == 0) sum = v;
+            else { sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w; }
+        }
+        if (ok) *reinterpret_cast<float4 *>(out + at) = sum;
+        else atomicExch(status, GF_STATUS_PEER_TIMEOUT);
     }
     // the last CTA of the call advances the epoch (after every CTA has read it)
     __syncthreads();
@@ -234,13 +310,15 @@ struct glmflash_ep {
     glmflash_config cfg;
     int rank = 0, world = 1, max_ctas = 0;
     unsigned char *local = nullptr;               // one allocation: recv | flags | epoch | done | status
-    size_t recv_bytes = 0, flag_bytes = 0, fin_bytes = 0, fin_flag_bytes = 0, win_flag_bytes = 0, total_bytes = 0;
-    size_t tail() const { return recv_bytes + flag_bytes + fin_bytes + fin_flag_bytes + win_flag_bytes; }   // epoch | done | status
+    size_t recv_bytes = 0, flag_bytes = 0, fin_bytes = 0, fin_flag_bytes = 0, win_flag_bytes = 0, ll_bytes = 0, total_bytes = 0;
+    size_t ll_offset() const { return recv_bytes + flag_bytes + fin_bytes + fin_flag_bytes + win_flag_bytes; }
+    size_t tail() const { return ll_offset() + ll_bytes; }   // epoch | done | status
     void *peer_base[EP_MAX_WORLD] = {};
     bool opened[EP_MAX_WORLD] = {};
     bool connected = false;
     float *out = nullptr;
     unsigned wait_polls = 2000000u;               // about a second of polling before a wait gives up
+    bool use_ll = true;                           // windows of <= 16 rows: flag-in-data words (GLMFLASH_EP_LL=0: fence + flag)
     bool bf16_rows = false;                       // windows of more than 16 rows: partials cross NVLink as bf16
 };
 
@@ -252,7 +330,8 @@ struct EpBlob {
     uint64_t config_hash;
 };
 static uint64_t ep_config_hash(const glmflash_config &c, int world) {
-    const int32_t f[8] = {GLMFLASH_ABI_VERSION, c.hidden, c.inter, c.experts, c.slots, c.max_rows, world, EP_THREADS};
+    constexpr int32_t EP_LAYOUT = 2;                          // bumped whenever the mapped area's layout or protocol changes
+    const int32_t f[8] = {GLMFLASH_ABI_VERSION * 256 + EP_LAYOUT, c.hidden, c.inter, c.experts, c.slots, c.max_rows, world, EP_THREADS};
     uint64_t h = 1469598103934665603ull;                      // FNV-1a
     for (size_t i = 0; i < sizeof(f); ++i) {
         h ^= reinterpret_cast<const unsigned char *>(f)[i];
@@ -270,6 +349,7 @@ extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int
     glmflash_ep *h = new (std::nothrow) glmflash_ep();
     GF_REQUIRE(h != nullptr, "out of host memory");
     h->cfg = *cfg; h->rank = rank; h->world = world;
+    if (const char *v = getenv("GLMFLASH_EP_LL")) h->use_ll = atoi(v) != 0;      // comparison runs
     const size_t H = cfg->hidden, R = cfg->max_rows;
     h->max_ctas = (int)(((H / 4 + EP_THREADS - 1) / EP_THREADS) * R);
     h->recv_bytes = (size_t)2 * world * R * H * 4;
@@ -278,6 +358,8 @@ extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int
     h->fin_flag_bytes = R > 16 ? ((size_t)2 * h->max_ctas * 4 + 255) / 256 * 256 : 0;
     // arrival words of the one-launch layer kernel's exchange (windows of <= 16 rows): [2][world][R][H / 128]
     h->win_flag_bytes = R <= 16 ? ((size_t)2 * world * R * (H / 128) * 4 + 255) / 256 * 256 : 0;
+    // {value, epoch} words of the flag-in-data exchange (windows of <= 16 rows): [2][world][R][H] x 8 bytes
+    h->ll_bytes = R <= 16 ? (size_t)2 * world * R * H * 8 : 0;
     h->total_bytes = h->tail() + 256;
     if (cudaMalloc((void **)&h->local, h->total_bytes) != cudaSuccess || cudaMemset(h->local, 0, h->total_bytes) != cudaSuccess ||
         cudaMalloc((void **)&h->out, R * H * 4) != cudaSuccess) {
@@ -344,6 +426,7 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
         peers.flags[k] = (unsigned *)((unsigned char *)h->peer_base[k] + h->recv_bytes);
         peers.fin[k] = (float *)((unsigned char *)h->peer_base[k] + h->recv_bytes + h->flag_bytes);
         peers.fin_flags[k] = (unsigned *)((unsigned char *)h->peer_base[k] + h->recv_bytes + h->flag_bytes + h->fin_bytes);
+        peers.ll[k] = (uint2 *)((unsigned char *)h->peer_base[k] + h->ll_offset());
     }
     unsigned *epoch = (unsigned *)(h->local + h->tail());
     const dim3 grid((unsigned)((c.hidden / 4 + EP_THREADS - 1) / EP_THREADS), (unsigned)rows);
@@ -352,6 +435,10 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
                         h->out, peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas,
                         c.slots, c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi,
                         h->wait_polls);
+    if (h->ll_bytes && h->use_ll)
+        return launch_k(ep_combine_ll_kernel, grid, dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w, h->out,
+                        peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, c.slots, c.hidden,
+                        c.experts, shared_here, c.expert_lo, c.expert_hi, h->wait_polls);
     return launch_k(ep_combine_kernel, grid, dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w, h->out,
                     peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas, c.slots,
                     c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi, h->wait_polls);
