@@ -666,7 +666,7 @@ def main():
                "router": "on device, inside the timed layer" if args.router else "routing table is an input",
                "layer_kernels": args.layer_kernels}
         for k in ("us_per_layer", "stack_tokens_per_s", "graph", "tflops", "e2e_per_layer_host_call", "roofline", "cpu_baseline", "oracle_check",
-                  "phases_us_per_layer", "ep_check", "distinct_experts_per_layer", "upstream_kernels_sm100a"):
+                  "phases_us_per_layer", "ep_check", "exchange_bf16", "distinct_experts_per_layer", "upstream_kernels_sm100a"):
             if k in head:
                 out[k] = head[k]
         out.setdefault("roofline", None)

@@ -18,6 +18,7 @@
 // adds the slots in rank order and stores the finished row into every rank's result buffer, and every rank waits for
 // that.  Per rank about 2 x rows x H x 4 bytes cross NVLink instead of world x that (268 MB at 4096 rows on 8 GPUs);
 // with glmflash_ep_set_exchange_bf16 the first of the two steps moves bf16 (1.5 x rows x H x 4 bytes in all).
+// (the owner stores them straight into the peers' output rows, which live inside the mapped area).
 // Receive buffers are double-buffered by epoch parity; the epoch lives in device memory and is advanced by the
 // last CTA of a call, so captured graphs replay correctly.  A wait that gives up sets the status word (the
 // analogue of upstream's poison word, native/roce.cu:127-141) and the kernel returns; nothing spins unbounded.
@@ -44,7 +45,7 @@ __device__ __forceinline__ void st_release_sys(unsigned *p, unsigned v) {
 struct EpPeers {
     float *recv[EP_MAX_WORLD];          // recv[k]: rank k's receive buffer [2][world][max_rows][H] (peer-mapped)
     unsigned *flags[EP_MAX_WORLD];      // flags[k]: rank k's flags [2][world][max_ctas]
-    float *fin[EP_MAX_WORLD];           // fin[k]: rank k's finished rows [2][max_rows][H]          (two-step form)
+    float *fin[EP_MAX_WORLD];           // fin[k]: rank k's output rows [max_rows][H]               (two-step form)
     unsigned *fin_flags[EP_MAX_WORLD];  // fin_flags[k]: rank k's [2][max_ctas]                     (two-step form)
     uint2 *ll[EP_MAX_WORLD];            // ll[k]: rank k's {value, epoch} words [2][world][max_rows][H]  (<= 16 rows)
 };
@@ -276,23 +277,17 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const floa
                     const float4 v = slot_value(k);
                     sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
                 }
-                for (int k = 0; k < world; ++k)
-                    *reinterpret_cast<float4 *>(peers.fin[k] + (size_t)par * slot_elems + off) = sum;
+                for (int k = 0; k < world; ++k) *reinterpret_cast<float4 *>(peers.fin[k] + off) = sum;
             }
         __threadfence_system();
         __syncthreads();
         if (threadIdx.x < world && ok_sh) st_release_sys(peers.fin_flags[threadIdx.x] + (size_t)par * max_ctas + chunk, epoch);
     }
-    // 3. everyone waits for the finished chunk and copies it to the output
+    // 3. everyone waits for the finished chunk: its owner has stored it straight into this rank's output rows.  (The
+    //    output needs no second buffer: an owner finishes a chunk of the NEXT call only after this rank's partial of that
+    //    call, which this rank sends after everything it enqueued behind this call -- the readers of the output -- has run.)
     if (threadIdx.x == 0)
         if (!ep_wait(peers.fin_flags[rank] + (size_t)par * max_ctas + chunk, epoch, wait_polls, status)) ok_sh = 0;
-    __syncthreads();
-    if (ok_sh)
-        for (int i = threadIdx.x; i < items; i += EP_THREADS) {
-            const size_t off = (size_t)(r0 + i / q4) * H + (i % q4) * 4;
-            *reinterpret_cast<float4 *>(out + off) =
-                __ldcg(reinterpret_cast<const float4 *>(peers.fin[rank] + (size_t)par * slot_elems + off));
-        }
     __syncthreads();
     if (threadIdx.x == 0) {
         if (atomicAdd(done_ptr, 1u) == gridDim.x - 1u) {
@@ -330,7 +325,7 @@ struct EpBlob {
     uint64_t config_hash;
 };
 static uint64_t ep_config_hash(const glmflash_config &c, int world) {
-    constexpr int32_t EP_LAYOUT = 2;                          // bumped whenever the mapped area's layout or protocol changes
+    constexpr int32_t EP_LAYOUT = 3;                          // bumped whenever the mapped area's layout or protocol changes
     const int32_t f[8] = {GLMFLASH_ABI_VERSION * 256 + EP_LAYOUT, c.hidden, c.inter, c.experts, c.slots, c.max_rows, world, EP_THREADS};
     uint64_t h = 1469598103934665603ull;                      // FNV-1a
     for (size_t i = 0; i < sizeof(f); ++i) {
@@ -354,7 +349,8 @@ extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int
     h->max_ctas = (int)(((H / 4 + EP_THREADS - 1) / EP_THREADS) * R);
     h->recv_bytes = (size_t)2 * world * R * H * 4;
     h->flag_bytes = ((size_t)2 * world * h->max_ctas * 4 + 255) / 256 * 256;
-    h->fin_bytes = R > 16 ? (size_t)2 * R * H * 4 : 0;        // the two-step form serves windows of more than 16 rows
+    h->fin_bytes = R > 16 ? (size_t)R * H * 4 : 0;            // the two-step form (windows of more than 16 rows) keeps its
+                                                              // output rows inside the mapped area: owners store into them
     h->fin_flag_bytes = R > 16 ? ((size_t)2 * h->max_ctas * 4 + 255) / 256 * 256 : 0;
     // arrival words of the one-launch layer kernel's exchange (windows of <= 16 rows): [2][world][R][H / 128]
     h->win_flag_bytes = R <= 16 ? ((size_t)2 * world * R * (H / 128) * 4 + 255) / 256 * 256 : 0;
@@ -362,10 +358,11 @@ extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int
     h->ll_bytes = R <= 16 ? (size_t)2 * world * R * H * 8 : 0;
     h->total_bytes = h->tail() + 256;
     if (cudaMalloc((void **)&h->local, h->total_bytes) != cudaSuccess || cudaMemset(h->local, 0, h->total_bytes) != cudaSuccess ||
-        cudaMalloc((void **)&h->out, R * H * 4) != cudaSuccess) {
+        (!h->fin_bytes && cudaMalloc((void **)&h->out, R * H * 4) != cudaSuccess)) {
         glmflash_ep_free(h);
         return fail("cudaMalloc(ep buffers) failed");
     }
+    if (h->fin_bytes) h->out = (float *)(h->local + h->recv_bytes + h->flag_bytes);
     h->peer_base[rank] = h->local;
     if (world == 1) h->connected = true;
     *out = h;
@@ -376,7 +373,8 @@ extern "C" void glmflash_ep_free(glmflash_ep *h) {
     if (!h) return;
     for (int k = 0; k < h->world; ++k)
         if (h->opened[k]) cudaIpcCloseMemHandle(h->peer_base[k]);
-    cudaFree(h->local); cudaFree(h->out);
+    if (!h->fin_bytes) cudaFree(h->out);
+    cudaFree(h->local);
     delete h;
 }
 
