@@ -218,7 +218,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_ll_kernel(const float *
 // BF16: the partials of step 1 cross NVLink as bf16 (upstream casts every rank's rows to bf16 before its gather and adds
 // them in fp32, src/batch.rs:651-658); every rank's partial, the owner's own included, takes the same rounding, so the
 // sum still depends on nothing but the rank order.  The finished rows of step 2 stay fp32.
-constexpr int EP_RB = 8;
+constexpr int EP_RB_MAX = 32;
 __device__ __forceinline__ uint2 ep_pack_bf16(const float4 v) {
     const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
     return make_uint2(*reinterpret_cast<const uint32_t *>(&a), *reinterpret_cast<const uint32_t *>(&b));
@@ -228,13 +228,13 @@ __device__ __forceinline__ float4 ep_unpack_bf16(const uint2 w) {
                        __uint_as_float(w.y & 0xffff0000u));
 }
 template <bool BF16>
-__global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
+__global__ void __launch_bounds__(EP_THREADS, 4) ep_exchange_rows_kernel(const float *__restrict__ Y, const int *__restrict__ picks,
                                                                       const float *__restrict__ route_w, float *__restrict__ out,
                                                                       EpPeers peers, unsigned *epoch_ptr, unsigned *done_ptr,
                                                                       int *status, int rank, int world, int rows, int max_rows,
                                                                       int max_ctas, int slots, int H, int E, int shared_exl3,
                                                                       int e_lo, int e_hi, int srow_lo, int srow_hi,
-                                                                      unsigned wait_polls) {
+                                                                      unsigned wait_polls, int EP_RB) {
     pdl_wait();
     pdl_launch_dependents();
     __shared__ int ok_sh;
@@ -245,13 +245,43 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const floa
     const int chunks = (rows + EP_RB - 1) / EP_RB, per = (chunks + world - 1) / world;
     const int owner = chunk / per;                            // < world because chunk < chunks
     const int q4 = H >> 2, items = (r1 - r0) * q4;            // float4 pieces of the chunk
-    // 1. this rank's partial of the chunk goes to the owner's slot `rank`
-    for (int i = threadIdx.x; i < items; i += EP_THREADS) {
-        const int r = r0 + i / q4, d = (i % q4) * 4;
-        const float4 acc = ep_partial(Y, picks, route_w, r, d, slots, H, E, shared_exl3, e_lo, e_hi, srow_lo, srow_hi);
+    // 1. this rank's partial of the chunk goes to the owner's slot `rank`.  Which pairs of a row are this rank's is looked
+    //    up once per (row, slot) into shared memory; a thread then has the loads of all its pairs of a piece in flight
+    //    together (the decision is uniform over a warp: a warp works on one row), and adds them in ep_partial's order.
+    __shared__ unsigned char take_sh[EP_RB_MAX][32];               // 1: pair (row, slot) is this rank's
+    for (int i = threadIdx.x; i < (r1 - r0) * slots; i += EP_THREADS) {
+        const int r = r0 + i / slots, sl = i % slots;
+        const int e = picks[r * slots + sl];
+        bool skip = e < 0 || e > E || (e == E ? !shared_exl3 : (e < e_lo || e >= e_hi));
+        if (e == E && srow_hi > srow_lo && (r < srow_lo || r >= srow_hi)) skip = true;
+        take_sh[i / slots][sl] = skip ? 0 : 1;
+    }
+    __syncthreads();
+    {
         float *slot = peers.recv[owner] + ((size_t)par * world + rank) * slot_elems;
-        if (BF16) *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(slot) + (size_t)r * H + d) = ep_pack_bf16(acc);
-        else *reinterpret_cast<float4 *>(slot + (size_t)r * H + d) = acc;
+#pragma unroll 2
+        for (int i = threadIdx.x; i < items; i += EP_THREADS) {
+            const int rl = i / q4, r = r0 + rl, d = (i % q4) * 4;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s0 = 0; s0 < slots; s0 += 8) {
+                float4 y[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (s0 + j < slots && take_sh[rl][s0 + j])
+                        y[j] = __ldcs(reinterpret_cast<const float4 *>(Y + ((size_t)r * slots + s0 + j) * H + d));
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (s0 + j >= slots || !take_sh[rl][s0 + j]) continue;
+                    if (s0 + j == slots - 1) { acc.x += y[j].x; acc.y += y[j].y; acc.z += y[j].z; acc.w += y[j].w; }
+                    else {
+                        const float w = route_w[r * slots + s0 + j];
+                        acc.x += w * y[j].x; acc.y += w * y[j].y; acc.z += w * y[j].z; acc.w += w * y[j].w;
+                    }
+                }
+            }
+            if (BF16) *reinterpret_cast<uint2 *>(reinterpret_cast<__nv_bfloat16 *>(slot) + (size_t)r * H + d) = ep_pack_bf16(acc);
+            else *reinterpret_cast<float4 *>(slot + (size_t)r * H + d) = acc;
+        }
     }
     __threadfence_system();
     __syncthreads();
@@ -263,6 +293,7 @@ __global__ void __launch_bounds__(EP_THREADS) ep_exchange_rows_kernel(const floa
             if (!ep_wait(peers.flags[rank] + ((size_t)par * world + threadIdx.x) * max_ctas + chunk, epoch, wait_polls, status)) ok_sh = 0;
         __syncthreads();
         if (ok_sh)
+#pragma unroll 2
             for (int i = threadIdx.x; i < items; i += EP_THREADS) {
                 const size_t off = (size_t)(r0 + i / q4) * H + (i % q4) * 4;
                 const float *base = peers.recv[rank] + (size_t)par * world * slot_elems;
@@ -313,6 +344,7 @@ struct glmflash_ep {
     bool connected = false;
     float *out = nullptr;
     unsigned wait_polls = 2000000u;               // about a second of polling before a wait gives up
+    int chunk_rows = 8;                           // rows per chunk of the two-step form (every rank the same)
     bool use_ll = true;                           // windows of <= 16 rows: flag-in-data words (GLMFLASH_EP_LL=0: fence + flag)
     bool bf16_rows = false;                       // windows of more than 16 rows: partials cross NVLink as bf16
 };
@@ -324,9 +356,9 @@ struct EpBlob {
     cudaIpcMemHandle_t mem;
     uint64_t config_hash;
 };
-static uint64_t ep_config_hash(const glmflash_config &c, int world) {
-    constexpr int32_t EP_LAYOUT = 3;                          // bumped whenever the mapped area's layout or protocol changes
-    const int32_t f[8] = {GLMFLASH_ABI_VERSION * 256 + EP_LAYOUT, c.hidden, c.inter, c.experts, c.slots, c.max_rows, world, EP_THREADS};
+static uint64_t ep_config_hash(const glmflash_config &c, int world, int chunk_rows, bool use_ll) {
+    constexpr int32_t EP_LAYOUT = 4;                          // bumped whenever the mapped area's layout or protocol changes
+    const int32_t f[8] = {GLMFLASH_ABI_VERSION * 256 + EP_LAYOUT, c.hidden, c.inter, c.experts, c.slots, c.max_rows, world, EP_THREADS | chunk_rows << 12 | (use_ll ? 1 << 20 : 0)};
     uint64_t h = 1469598103934665603ull;                      // FNV-1a
     for (size_t i = 0; i < sizeof(f); ++i) {
         h ^= reinterpret_cast<const unsigned char *>(f)[i];
@@ -345,6 +377,7 @@ extern "C" int glmflash_ep_new(const glmflash_config *cfg, size_t cfg_bytes, int
     GF_REQUIRE(h != nullptr, "out of host memory");
     h->cfg = *cfg; h->rank = rank; h->world = world;
     if (const char *v = getenv("GLMFLASH_EP_LL")) h->use_ll = atoi(v) != 0;      // comparison runs
+    if (const char *v = getenv("GLMFLASH_EP_CHUNK_ROWS")) h->chunk_rows = std::min(std::max(atoi(v), 1), EP_RB_MAX);
     const size_t H = cfg->hidden, R = cfg->max_rows;
     h->max_ctas = (int)(((H / 4 + EP_THREADS - 1) / EP_THREADS) * R);
     h->recv_bytes = (size_t)2 * world * R * H * 4;
@@ -382,7 +415,7 @@ extern "C" int glmflash_ep_get_handle(glmflash_ep *h, void *handle_out) {
     GF_REQUIRE(h && handle_out, "null argument");
     EpBlob b{};
     GF_CUDA(cudaIpcGetMemHandle(&b.mem, h->local));
-    b.config_hash = ep_config_hash(h->cfg, h->world);
+    b.config_hash = ep_config_hash(h->cfg, h->world, h->chunk_rows, h->use_ll);
     memcpy(handle_out, &b, sizeof(b));
     return 0;
 }
@@ -391,7 +424,7 @@ extern "C" int glmflash_ep_connect(glmflash_ep *h, const void *all_handles) {
     GF_REQUIRE(h && all_handles, "null argument");
     GF_REQUIRE(!h->connected, "already connected");
     const unsigned char *p = (const unsigned char *)all_handles;
-    const uint64_t mine = ep_config_hash(h->cfg, h->world);
+    const uint64_t mine = ep_config_hash(h->cfg, h->world, h->chunk_rows, h->use_ll);
     for (int k = 0; k < h->world; ++k) {                      // every rank's blob is checked before any mapping is made
         EpBlob b;
         memcpy(&b, p + (size_t)k * sizeof(b), sizeof(b));
@@ -429,10 +462,11 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
     unsigned *epoch = (unsigned *)(h->local + h->tail());
     const dim3 grid((unsigned)((c.hidden / 4 + EP_THREADS - 1) / EP_THREADS), (unsigned)rows);
     if (rows > 16 && h->world > 1)
-        return launch_k(h->bf16_rows ? ep_exchange_rows_kernel<true> : ep_exchange_rows_kernel<false>, dim3((unsigned)((rows + EP_RB - 1) / EP_RB)), dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w,
-                        h->out, peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, h->max_ctas,
-                        c.slots, c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo, c.shared_row_hi,
-                        h->wait_polls);
+        return launch_k(h->bf16_rows ? ep_exchange_rows_kernel<true> : ep_exchange_rows_kernel<false>,
+                        dim3((unsigned)((rows + h->chunk_rows - 1) / h->chunk_rows)), dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0,
+                        Y, picks, route_w, h->out, peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows,
+                        h->max_ctas, c.slots, c.hidden, c.experts, shared_here, c.expert_lo, c.expert_hi, c.shared_row_lo,
+                        c.shared_row_hi, h->wait_polls, h->chunk_rows);
     if (h->ll_bytes && h->use_ll)
         return launch_k(ep_combine_ll_kernel, grid, dim3(EP_THREADS), 0, (cudaStream_t)stream, c.pdl != 0, Y, picks, route_w, h->out,
                         peers, epoch, epoch + 1, (int *)(epoch + 2), h->rank, h->world, rows, c.max_rows, c.slots, c.hidden,
