@@ -153,7 +153,10 @@ int experts_run_fused(glmflash_experts *e, cudaStream_t s, const glmflash_weight
     GF_REQUIRE(((uintptr_t)input | (uintptr_t)w->suh_g | (uintptr_t)w->suh_u) % 8 == 0, "input and scale vectors must be 8-byte aligned");
     const bool pdl = c.pdl != 0;
     const int H = c.hidden, I = c.inter, P = rows * c.slots, E1 = c.experts + 1;
-    const int umax = std::min(rows * (c.slots - 1) + 1, E1);
+    // clusters per column block: the distinct experts of the window that THIS GPU computes, at most its expert window
+    // (+ the shared expert) -- an expert-parallel rank does not launch CTAs for the other ranks' experts
+    const int mine = (c.expert_hi - c.expert_lo) + (c.shared_exl3 ? 1 : 0);
+    const int umax = std::max(1, std::min(std::min(rows * (c.slots - 1) + 1, E1), mine));
     GemvArgs a{};
     a.status = e->status;
     a.P = P; a.maxm = rows; a.slots = c.slots; a.E = c.experts; a.e_lo = c.expert_lo; a.e_hi = c.expert_hi;

@@ -175,17 +175,21 @@ __device__ __forceinline__ int gemv_item(const GemvArgs &a, unsigned char *smem,
     if (a.picks && a.rows == 1) {
         // ---- one row: the distinct experts are the row's picks in ascending order; every warp finds number u itself
         //      (one load, a few shuffles, no block barrier).  A pick that repeats an earlier slot does not count.
-        const int pk = lane < a.slots ? __ldcg(a.picks + lane) : 0x7fffffff;
+        //      Only experts this GPU computes count (expert window, shared-expert switch), so that the launch needs no
+        //      more clusters than the window has experts.
+        constexpr int NONE = 0x7fffffff;
+        int pk = lane < a.slots ? __ldcg(a.picks + lane) : NONE;
+        if (pk != NONE && expert_skipped(pk, a.E, a.shared_exl3, a.e_lo, a.e_hi)) pk = NONE;
         bool dup = false;
         int rank_lt = 0, distinct = 0;
         for (int j = 0; j < a.slots; ++j) {
             const int v = __shfl_sync(0xffffffffu, pk, j);
-            bool vdup = false;
+            bool vdup = v == NONE;
             for (int q = 0; q < j; ++q) vdup |= __shfl_sync(0xffffffffu, pk, q) == v;
             if (j < lane && v == pk) dup = true;
             if (!vdup) { distinct++; if (v < pk) rank_lt++; }
         }
-        const uint32_t hit = __ballot_sync(0xffffffffu, lane < a.slots && !dup && rank_lt == u);
+        const uint32_t hit = __ballot_sync(0xffffffffu, pk != NONE && !dup && rank_lt == u);
         GF_STAMP(14);
         cnt = distinct;
         const int slot = hit ? __ffs(hit) - 1 : 0;
@@ -201,7 +205,8 @@ __device__ __forceinline__ int gemv_item(const GemvArgs &a, unsigned char *smem,
         const int np = a.rows * a.slots;
         for (int i = tid; i < np; i += GEMV_THREADS) {
             const int pk = __ldcg(a.picks + i);
-            if (pk >= 0 && pk <= a.E) atomicOr(&used_sh[pk >> 5], 1u << (pk & 31));   // ids above E name nothing
+            // ids above E name nothing; experts another GPU computes do not count (see the one-row form)
+            if (!expert_skipped(pk, a.E, a.shared_exl3, a.e_lo, a.e_hi)) atomicOr(&used_sh[pk >> 5], 1u << (pk & 31));
         }
         __syncthreads();
         __shared__ int e_sh, cnt_sh;

@@ -133,6 +133,23 @@ def test_expert_windows_sum_to_the_layer(pkg, synth, cuda, banks):
     assert rel_err(lo + hi, full)[0] < 1e-5
 
 
+@pytest.mark.parametrize("launches", [3, 1])
+@pytest.mark.parametrize("rows", [1, 7, 16])
+def test_eight_expert_windows_sum_to_the_layer(pkg, synth, cuda, banks, launches, rows):
+    """The partials of eight ranks (eight routed experts each, the shared expert on rank `rows % 8`) add up to the layer.
+    A rank launches clusters for its own experts only, so its kernels must number the window's experts among ITS experts."""
+    _, dev = banks
+    x = synth.activations_bf16(71 + rows, rows, H)
+    picks, rw = synth.route(72 + rows, rows, E, S - 1, shared_bias=rows > 1)
+    full = _run(_moe(pkg, launches, hidden=H, inter=I, experts=E, slots=S, max_rows=16), dev["scaled"], x, picks, rw, rows, cuda)
+    total = np.zeros_like(full)
+    for r in range(8):
+        part = _run(_moe(pkg, launches, hidden=H, inter=I, experts=E, slots=S, max_rows=16, expert_lo=8 * r, expert_hi=8 * r + 8,
+                         shared_exl3=int(r == rows % 8)), dev["scaled"], x, picks, rw, rows, cuda)
+        total += part
+    assert rel_err(total, full)[0] < 1e-5
+
+
 def test_small_and_odd_shapes_vs_oracle(pkg, oracle, synth, cuda):
     """Shapes other than the benchmark's: one split per projection, and a hidden size (2304) that is not a power of
     two times 256 (nine splits in the layer kernel, 6 x 24 k-tiles in the table-driven kernels)."""
