@@ -66,10 +66,10 @@ def host_threads():
         return max(1, os.cpu_count() or 1)
 
 
-def recorded_traffic(key):
+def recorded_traffic(key, path=None):
     """DRAM bytes of one launch of the dominant kernel from the last ncu capture (profiles/traffic.json), or None when
     the kernel source has changed since that capture."""
-    p = os.path.join(ROOT, "profiles", "traffic.json")
+    p = path or os.path.join(ROOT, "profiles", "traffic.json")
     if not os.path.exists(p):
         return None
     rec = json.load(open(p)).get(key)
@@ -85,7 +85,7 @@ TRAFFIC_SOURCES = {"gemv": "glm-flash-rs_b200/csrc/gemv.cuh", "window": "glm-fla
                    "fast": "glm-flash-rs_b200/csrc/fast_experts.cu"}
 
 
-def record_traffic(csv_path, key, kernel_regex, command):
+def record_traffic(csv_path, key, kernel_regex, command, out=None):
     """Summary step of an ncu capture: read the `--csv` log of a run that collected dram__bytes_read.sum and
     dram__bytes_write.sum, average read + write per launch over the kernels whose name matches, and store the figure in
     profiles/traffic.json under `key`, with the hash of the kernel source it was measured on and the capture's command.
@@ -106,7 +106,7 @@ def record_traffic(csv_path, key, kernel_regex, command):
     rd = sum(d["dram__bytes_read.sum"] for d in full) / len(full)
     wr = sum(d["dram__bytes_write.sum"] for d in full) / len(full)
     source = TRAFFIC_SOURCES[key.split("_")[0]]
-    out = os.path.join(ROOT, "profiles", "traffic.json")
+    out = out or os.path.join(ROOT, "profiles", "traffic.json")
     table = json.load(open(out)) if os.path.exists(out) else {}
     table[key] = {"traffic_bytes": round(rd + wr), "dram_read_bytes": round(rd), "dram_write_bytes": round(wr), "launches": len(full),
                   "kernel": kernel_regex, "source": source,
@@ -234,11 +234,20 @@ class Bench:
         self.failures = []
 
     # ---- timing: K steps between CUDA events on the launching stream, barrier + synchronise on both sides, max over ranks
-    def timed(self, fn, steps, warmup):
+    def timed(self, fn, steps, warmup, guard=None):
+        """guard: an owner with check() (EpMoe).  A device status word that is set after the first warm-up step means every
+        further step would sit out its bounded waits (seconds each): the run stops there instead of timing garbage."""
         torch, dist = self.torch, self.dist
         with torch.cuda.stream(self.stream):
-            for _ in range(warmup):
+            for k in range(warmup):
                 fn()
+                if k == 0 and guard is not None:
+                    self.stream.synchronize()
+                    try:
+                        guard.check()
+                    except self.pkg.GlmFlashError as ex:
+                        print(f"bench: rank {self.rank}: {ex} after the first step; stopping", file=sys.stderr, flush=True)
+                        os._exit(3)
             self.stream.synchronize()
             if self.world > 1:
                 dist.barrier()
@@ -339,7 +348,7 @@ class Bench:
             for l in range(L):
                 layer(l, True)
         g = self.graph_of(step_eager)
-        ms_step = self.timed((lambda: g.replay()) if g is not None else step_eager, steps, warmup)
+        ms_step = self.timed((lambda: g.replay()) if g is not None else step_eager, steps, warmup, guard=epm)
         self.check_status(epm, f"decode rows={rows}")
         value = rows * L / (ms_step / 1e3)
 
@@ -460,7 +469,7 @@ class Bench:
             l = state["i"] % L
             state["i"] += 1
             epm.run(l, self.structs[l], x_d[l], p_d[l], w_d[l], rows)
-        ms_step = self.timed(step, steps, warmup)
+        ms_step = self.timed(step, steps, warmup, guard=epm)
         self.check_status(epm, f"prefill rows={rows}")
         flops = rows * S * 3 * 2 * H * I                               # all pairs incl. the shared expert, three matrices
         xh = torch.from_numpy(xs.view(np.int16)).pin_memory()
