@@ -175,24 +175,36 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_ll_kernel(const float *
             st_volatile_v4(dst, __float_as_uint(acc.x), epoch, __float_as_uint(acc.y), epoch);
             st_volatile_v4(dst + 2, __float_as_uint(acc.z), epoch, __float_as_uint(acc.w), epoch);
         }
-        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+        // all peers' words are requested together and only the late ones are asked for again: the wait costs one local
+        // round trip after the last arrival, not one per peer
+        uint4 lo[EP_MAX_WORLD], hi[EP_MAX_WORLD];
+        unsigned missing = ((1u << world) - 1u) & ~(1u << rank);
         bool ok = true;
-        for (int k = 0; k < world && ok; ++k) {
-            float4 v = acc;
-            if (k != rank) {
-                const uint2 *src = peers.ll[rank] + ((size_t)par * world + k) * slot_words + at;
-                uint4 lo = ld_volatile_v4(src), hi = ld_volatile_v4(src + 2);
-                for (unsigned i = 0; lo.y != epoch || lo.w != epoch || hi.y != epoch || hi.w != epoch; ++i) {
-                    if (i >= wait_polls) { ok = false; break; }
-                    if ((i & 1023u) == 1023u) {
-                        if (*reinterpret_cast<volatile int *>(status) == GF_STATUS_PEER_TIMEOUT) { ok = false; break; }
-                        __nanosleep(200);
-                    }
-                    lo = ld_volatile_v4(src);
-                    hi = ld_volatile_v4(src + 2);
-                }
-                v = make_float4(__uint_as_float(lo.x), __uint_as_float(lo.z), __uint_as_float(hi.x), __uint_as_float(hi.z));
+        for (unsigned i = 0; missing; ++i) {
+            if (i >= wait_polls) { ok = false; break; }
+            if ((i & 1023u) == 1023u) {
+                if (*reinterpret_cast<volatile int *>(status) == GF_STATUS_PEER_TIMEOUT) { ok = false; break; }
+                __nanosleep(200);
             }
+#pragma unroll
+            for (int k = 0; k < EP_MAX_WORLD; ++k)
+                if (missing >> k & 1u) {
+                    const uint2 *src = peers.ll[rank] + ((size_t)par * world + k) * slot_words + at;
+                    lo[k] = ld_volatile_v4(src);
+                    hi[k] = ld_volatile_v4(src + 2);
+                }
+#pragma unroll
+            for (int k = 0; k < EP_MAX_WORLD; ++k)
+                if ((missing >> k & 1u) && lo[k].y == epoch && lo[k].w == epoch && hi[k].y == epoch && hi[k].w == epoch)
+                    missing &= ~(1u << k);
+        }
+        float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int k = 0; k < EP_MAX_WORLD; ++k) {
+            if (k >= world) break;
+            const float4 v = k == rank ? acc
+                                       : make_float4(__uint_as_float(lo[k].x), __uint_as_float(lo[k].z), __uint_as_float(hi[k].x),
+                                                     __uint_as_float(hi[k].z));
             if (k == 0) sum = v;
             else { sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w; }
         }
