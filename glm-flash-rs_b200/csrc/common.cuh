@@ -165,10 +165,13 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parit
 }
 // Bounded wait: gives up after `limit` polls and reports false (the caller records an error status and
 // leaves); nothing in this library spins without a bound.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t limit = 4000000u) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, const int *status = nullptr, uint32_t limit = 4000000u) {
     if (mbar_try_wait(bar, parity)) return true;
-    for (uint32_t i = 0; i < limit; ++i)              // the waiting thread may sleep inside the instruction: no issue slots taken
+    for (uint32_t i = 0; i < limit; ++i) {            // the waiting thread may sleep inside the instruction: no issue slots taken
         if (mbar_try_wait_hint(bar, parity, 400u)) return true;
+        // a wait of this launch has already given up (the status word is set): do not sit out the limit in every CTA
+        if (status && (i & 255u) == 255u && *reinterpret_cast<const volatile int *>(status) != 0) return false;
+    }
     return false;
 }
 // 1-D TMA bulk copy global -> shared, completion counted in bytes on an mbarrier.  Both addresses and the

@@ -273,6 +273,8 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
     for (uint32_t i = 0; i < 400000u; ++i) {                  // each poll may sleep up to 10 us: at most about 4 s
         if (mbar_try_wait_hint(bar, parity, 10000u)) return true;
         if (*abort_flag) return false;
+        // another CTA of this launch has already given up: leave as well instead of sitting out the limit here too
+        if ((i & 15u) == 15u && *reinterpret_cast<volatile int *>(status) != 0) { *abort_flag = 1; return false; }
     }
     *abort_flag = 1;
     atomicExch(status, code);

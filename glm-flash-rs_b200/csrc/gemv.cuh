@@ -394,7 +394,7 @@ __device__ __forceinline__ int gemv_item(const GemvArgs &a, unsigned char *smem,
 #pragma unroll
             for (int m = 0; m < 8; ++m) b1[m] = *reinterpret_cast<const uint2 *>(ar + m * 8);
         }
-        if (!mbar_wait(bars + g, 0)) { ok = false; break; }
+        if (!mbar_wait(bars + g, 0, a.status)) { ok = false; break; }
         if (g == 0) GF_STAMP(5);
         const unsigned char *wrow = wsm + ((size_t)mat * KTC + 4 * g + T) * GEMV_WROW + nt0 * 128 + G * 16;
 #pragma unroll
