@@ -21,8 +21,12 @@ input row and routing table, as the stack is "experts only").
 N > 1: the 64 routed experts are split evenly over the ranks (expert parallel), the shared expert goes round robin over
 the layers (prefill: split by rows); every rank computes a partial layer output, and the ranks' partials are exchanged
 over NVLink and added in rank order (the reference's fixed-order sum after its all-gather) by the exchange kernel.
-Total work is fixed: "scaling": "strong".  Outside the timed region every rank also runs the whole window on its own and
-compares (ep_check); a failed check or a non-zero device status word makes the run exit non-zero.
+Total work is fixed: "scaling": "strong".  phases_us_per_layer splits a layer into the rank's own kernels and the exchange;
+outside the timed region every rank also runs the whole window on its own and compares (ep_check); a failed check or a
+non-zero device status word makes the run exit non-zero, and a status word that is set after the first step stops the run
+there.  Prefill at N > 1 also reports the exchange with bf16 partial rows (exchange_bf16, checked at a bf16 tolerance).
+roofline.traffic comes from profiles/traffic.json, which `bench.py --record-traffic NCU_CSV KEY KERNEL_REGEX COMMAND` writes
+from an ncu --csv log; it is null when the kernel source has changed since that capture.
 --impl reference: the reference's CPU path for the op (its scalar oracle restated in oracle/exl3_oracle.c; the Rust
 original cannot be built here) on all host threads, bounded samples of the same workload.
 """
