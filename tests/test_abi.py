@@ -63,3 +63,16 @@ def test_no_cpu_fallback(pkg):
     assert b"no CUDA device" in L.glmflash_error()
     with pytest.raises(pkg.GlmFlashError):
         pkg.ExpertGpu(cfg)
+
+
+def test_every_entry_point_is_declared_and_has_a_binding_line():
+    """The header, the ctypes table and the reference-side binding shown to maintainers name the same entry points."""
+    import re
+    from conftest import ROOT
+    import __graft_entry__ as entry
+    pkg = entry.load_package()
+    header = open(os.path.join(ROOT, "include", "glmflash_b200.h")).read()
+    stub = open(os.path.join(ROOT, "INTEGRATION.md")).read()
+    declared = set(re.findall(r"\b(glmflash_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(pkg.SYMBOLS), declared ^ set(pkg.SYMBOLS)
+    assert not [s for s in pkg.SYMBOLS if "fn " + s + "(" not in stub]
