@@ -424,7 +424,8 @@ class Bench:
         else:
             res["distinct_experts_per_layer"] = distinct
             # per-phase split of one layer: this rank's share without the exchange, and with it
-            solo = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows, expert_lo=epm.window[0], expert_hi=epm.window[1], shared_exl3=1))
+            solo = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows, expert_lo=epm.window[0], expert_hi=epm.window[1],
+                                           shared_exl3=2 if epm.dynamic else 1))
 
             def step_solo():
                 for l in range(L):

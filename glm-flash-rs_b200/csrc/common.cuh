@@ -124,6 +124,38 @@ __device__ __forceinline__ void fwht128(float (&v)[4], int lane) {
     }
 }
 
+// ---- the shared expert's owner, decided per window (config shared_exl3 == 2) -------------------------------
+// Expert-parallel ranks hold contiguous windows of W routed experts (rank = id / W).  When the shared expert's owner is
+// left to the device, it is the rank whose window holds the FEWEST distinct routed experts of the window's routing
+// table (ties: the lowest rank): the rank that would otherwise idle longest takes the expert every row uses.  Every rank
+// evaluates this on the same table, so all agree without an exchange, and the expert kernels and the combine /
+// exchange kernels of a rank agree with each other.  At most 32 ranks (one lane each).
+// `used`: bitmap (shared memory, 32 words) of the ids the table names.  Called by a whole warp; same result in every lane.
+__device__ __forceinline__ int shared_owner_rank(const uint32_t *used, int E, int W, int lane) {
+    const int G = (E + W - 1) / W;
+    int c = 1023;
+    if (lane < G) {
+        c = 0;
+        for (int e = lane * W; e < min(E, (lane + 1) * W); ++e) c += (used[e >> 5] >> (e & 31)) & 1u;
+    }
+    int best = c * 32 + lane;
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, d));
+    return best & 31;
+}
+// Block-level form for kernels that have no bitmap of their own: builds it from the routing table (np = rows x slots
+// entries) in `used` (32 words of shared memory) and returns the owner rank in every thread.  All threads of the block call.
+__device__ __forceinline__ int shared_owner_of_window(const int *picks, int np, int E, int W, uint32_t *used) {
+    if (threadIdx.x < 32) used[threadIdx.x] = 0u;
+    __syncthreads();
+    for (int i = threadIdx.x; i < np; i += blockDim.x) {
+        const int pk = picks[i];
+        if (pk >= 0 && pk < E) atomicOr(&used[pk >> 5], 1u << (pk & 31));
+    }
+    __syncthreads();
+    return shared_owner_rank(used, E, W, threadIdx.x & 31);
+}
+
 // ---- shared-memory addressing, TMA bulk copy, mbarrier -----------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 

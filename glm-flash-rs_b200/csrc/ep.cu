@@ -90,6 +90,9 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_kernel(const float *__r
                                                                 int max_ctas, int slots, int H, int E, int shared_exl3,
                                                                 int e_lo, int e_hi, int srow_lo, int srow_hi,
                                                                 unsigned wait_polls) {
+    // (the routing table was complete before the expert kernels in front ran: it may be read ahead of the dependency wait)
+    __shared__ uint32_t used_sh[32];
+    if (shared_exl3 == 2) shared_exl3 = shared_owner_of_window(picks, rows * slots, E, e_hi - e_lo, used_sh) == e_lo / (e_hi - e_lo);
     pdl_wait();
     pdl_launch_dependents();
     __shared__ int ok_sh;
@@ -159,6 +162,9 @@ __global__ void __launch_bounds__(EP_THREADS) ep_combine_ll_kernel(const float *
                                                                    int *status, int rank, int world, int rows, int max_rows,
                                                                    int slots, int H, int E, int shared_exl3, int e_lo, int e_hi,
                                                                    unsigned wait_polls) {
+    // (the routing table was complete before the expert kernels in front ran: it may be read ahead of the dependency wait)
+    __shared__ uint32_t used_sh[32];
+    if (shared_exl3 == 2) shared_exl3 = shared_owner_of_window(picks, rows * slots, E, e_hi - e_lo, used_sh) == e_lo / (e_hi - e_lo);
     pdl_wait();
     pdl_launch_dependents();
     const int r = blockIdx.y;
@@ -463,6 +469,10 @@ extern "C" int glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y,
     GF_REQUIRE(h->connected, "glmflash_ep_connect has not been called");
     GF_REQUIRE(rows > 0 && rows <= h->cfg.max_rows, "rows outside the scratch bound");
     const glmflash_config &c = h->cfg;
+    GF_REQUIRE(shared_here >= 0 && shared_here <= 2, "shared_here must be 0, 1 or 2");
+    GF_REQUIRE(shared_here != 2 || (rows <= 16 && c.expert_hi > c.expert_lo && c.expert_lo % (c.expert_hi - c.expert_lo) == 0 &&
+                                    (c.experts + c.expert_hi - c.expert_lo - 1) / (c.expert_hi - c.expert_lo) <= 32),
+               "shared_here = 2 (owner decided per window) needs a window of <= 16 rows and equal expert windows of at most 32 ranks");
     EpPeers peers{};
     for (int k = 0; k < h->world; ++k) {
         peers.recv[k] = (float *)h->peer_base[k];

@@ -62,6 +62,13 @@ int check_config(const glmflash_config *cfg, size_t cfg_bytes, int max_rows_limi
     GF_REQUIRE(cfg->expert_lo >= 0 && cfg->expert_hi <= cfg->experts && cfg->expert_lo <= cfg->expert_hi,
                "expert window must satisfy 0 <= lo <= hi <= experts");
     GF_REQUIRE(cfg->limit > 0.f, "limit must be positive");
+    GF_REQUIRE(cfg->shared_exl3 >= 0 && cfg->shared_exl3 <= 2, "shared_exl3 must be 0, 1 or 2");
+    if (cfg->shared_exl3 == 2) {
+        const int W = cfg->expert_hi - cfg->expert_lo;
+        GF_REQUIRE(cfg->max_rows <= 16, "shared_exl3 = 2 (owner decided per window) is for handles of <= 16 rows");
+        GF_REQUIRE(W > 0 && cfg->expert_lo % W == 0 && (cfg->experts + W - 1) / W <= 32,
+                   "shared_exl3 = 2 needs equal contiguous expert windows (expert_lo a multiple of the window size, at most 32 ranks)");
+    }
     GF_REQUIRE(cfg->shared_row_lo >= 0 && cfg->shared_row_lo <= cfg->shared_row_hi, "shared-expert row window must satisfy 0 <= lo <= hi");
     GF_REQUIRE(cfg->shared_row_hi == 0 || cfg->max_rows > 16, "a shared-expert row window needs a handle for more than 16 rows");
     int dev_count = 0;
@@ -110,6 +117,7 @@ extern "C" int glmflash_experts_run_rows(glmflash_experts *e, void *stream, cons
                                          const int32_t *members, int rows, int maxm) {
     GF_REQUIRE(e && w && input && picks && ids && count && members, "null argument");
     const glmflash_config &c = e->cfg;
+    GF_REQUIRE(c.shared_exl3 != 2, "shared_exl3 = 2 (owner decided per window) is served by the layer calls, not by run_rows");
     GF_REQUIRE(rows > 0 && rows <= c.max_rows && maxm >= rows && maxm <= c.max_rows, "expert verifier row/member bounds");
     GF_REQUIRE(x_stride >= c.hidden && x_stride % 4 == 0, "x_stride must be >= hidden and a multiple of 4");
     GF_REQUIRE(((uintptr_t)w->gt | (uintptr_t)w->ut | (uintptr_t)w->dt) % 16 == 0, "trellis tensors must be 16-byte aligned");

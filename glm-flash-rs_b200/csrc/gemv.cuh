@@ -179,7 +179,24 @@ __device__ __forceinline__ int gemv_item(const GemvArgs &a, unsigned char *smem,
         //      more clusters than the window has experts.
         constexpr int NONE = 0x7fffffff;
         int pk = lane < a.slots ? __ldcg(a.picks + lane) : NONE;
-        if (pk != NONE && expert_skipped(pk, a.E, a.shared_exl3, a.e_lo, a.e_hi)) pk = NONE;
+        int sh = a.shared_exl3;
+        if (sh == 2) {
+            // the shared expert goes to the rank with the fewest distinct routed picks of the row (shared_owner_rank's rule,
+            // evaluated on the row's picks held by the lanes)
+            const int W = a.e_hi - a.e_lo, ranks = (a.E + W - 1) / W;
+            int c = 0;
+            for (int j = 0; j < a.slots; ++j) {
+                const int v = __shfl_sync(0xffffffffu, pk, j);
+                bool vdup = false;
+                for (int q = 0; q < j; ++q) vdup |= __shfl_sync(0xffffffffu, pk, q) == v;
+                if (!vdup && v >= 0 && v < a.E && v / W == lane) c++;
+            }
+            int best = (lane < ranks ? c : 1023) * 32 + lane;
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) best = min(best, __shfl_xor_sync(0xffffffffu, best, d));
+            sh = (best & 31) == a.e_lo / W;
+        }
+        if (pk != NONE && expert_skipped(pk, a.E, sh, a.e_lo, a.e_hi)) pk = NONE;
         bool dup = false;
         int rank_lt = 0, distinct = 0;
         for (int j = 0; j < a.slots; ++j) {
@@ -205,13 +222,19 @@ __device__ __forceinline__ int gemv_item(const GemvArgs &a, unsigned char *smem,
         const int np = a.rows * a.slots;
         for (int i = tid; i < np; i += GEMV_THREADS) {
             const int pk = __ldcg(a.picks + i);
-            // ids above E name nothing; experts another GPU computes do not count (see the one-row form)
-            if (!expert_skipped(pk, a.E, a.shared_exl3, a.e_lo, a.e_hi)) atomicOr(&used_sh[pk >> 5], 1u << (pk & 31));
+            if (pk >= 0 && pk <= a.E) atomicOr(&used_sh[pk >> 5], 1u << (pk & 31));   // ids above E name nothing
         }
         __syncthreads();
         __shared__ int e_sh, cnt_sh;
         if (warp == 0) {                                       // number u among the set bits: one bitmap word per lane
-            const uint32_t bts = used_sh[lane];
+            // experts another GPU computes do not count (see the one-row form): the expert window, and the shared expert
+            // by the config's switch or, when its owner is decided per window, by shared_owner_rank
+            int sh = a.shared_exl3;
+            if (sh == 2) sh = shared_owner_rank(used_sh, a.E, a.e_hi - a.e_lo, lane) == a.e_lo / (a.e_hi - a.e_lo);
+            const int lo = min(max(a.e_lo - 32 * lane, 0), 32), hi = min(max(a.e_hi - 32 * lane, 0), 32);
+            uint32_t keep = hi > lo ? ((hi == 32 ? 0xffffffffu : (1u << hi) - 1u) & ~((1u << lo) - 1u)) : 0u;
+            if (sh && (a.E >> 5) == lane) keep |= 1u << (a.E & 31);
+            const uint32_t bts = used_sh[lane] & keep;
             const int c = __popc(bts);
             int incl = c;
 #pragma unroll

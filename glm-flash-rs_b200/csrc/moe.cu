@@ -25,6 +25,8 @@ __global__ void __launch_bounds__(256) combine_kernel(const float *__restrict__ 
     const int d = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     __shared__ float wgt_sh[32];
     __shared__ uint32_t live_sh;
+    __shared__ uint32_t used_sh[32];
+    if (shared_exl3 == 2) shared_exl3 = shared_owner_of_window(picks, rows * slots, E, e_hi - e_lo, used_sh) == e_lo / (e_hi - e_lo);
     if (threadIdx.x < 32) {
         const int s = threadIdx.x;
         bool keep = false;
@@ -169,12 +171,15 @@ extern "C" int glmflash_moe_run_ep(glmflash_moe *m, glmflash_ep *ep, void *strea
         return experts_run_window(m->experts, (cudaStream_t)stream, w, input, x_stride, picks, route_w, rows, result,
                                   peers.world > 1 ? &peers : nullptr, shared_here);
     }
+    const int shared = shared_here < 0 ? m->cfg.shared_exl3 : shared_here;
+    GF_REQUIRE((shared == 2) == (m->cfg.shared_exl3 == 2),
+               "the shared expert's owner is decided per window (2) either by both the layer owner and the call, or by neither");
     const int saved = m->phases;
     m->phases &= ~16;                               // experts only: the combine is the exchange kernel's first step
     const int rc = glmflash_moe_run(m, stream, w, input, x_stride, picks, route_w, rows);
     m->phases = saved;
     if (rc) return -1;
-    return glmflash_ep_combine(ep, stream, glmflash_moe_pairs(m), picks, route_w, rows, shared_here < 0 ? m->cfg.shared_exl3 : shared_here);
+    return glmflash_ep_combine(ep, stream, glmflash_moe_pairs(m), picks, route_w, rows, shared);
 }
 
 extern "C" int glmflash_moe_set_phases(glmflash_moe *m, int mask) {

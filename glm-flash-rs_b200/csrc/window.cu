@@ -941,7 +941,9 @@ __global__ void __launch_bounds__(WIN_THREADS, 1) window_kernel(const __grid_con
 
 bool experts_window_supported(const glmflash_config &c, int rows) {
     const int umax = std::min(rows * (c.slots - 1) + 1, c.experts + 1);
-    return rows >= 1 && rows <= 16 && rows * c.slots <= 512 && umax <= WIN_UMAX && c.hidden <= 8192 && c.inter <= 8192;
+    // (an owner of the shared expert that is decided per window, shared_exl3 == 2, is served by the three-launch kernels)
+    return rows >= 1 && rows <= 16 && rows * c.slots <= 512 && umax <= WIN_UMAX && c.hidden <= 8192 && c.inter <= 8192 &&
+           c.shared_exl3 != 2;
 }
 
 size_t experts_window_sync_words(const glmflash_config &c) { return win_sync_words(c.experts, c.hidden, c.inter); }

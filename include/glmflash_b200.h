@@ -52,7 +52,11 @@ typedef struct glmflash_config {
     int32_t slots;         /* S: top-k + 1 (upstream 9; benchmark 5), at most 32                            */
     int32_t max_rows;      /* scratch capacity in rows                                                     */
     int32_t shared_exl3;   /* 1: the shared expert (id E) is an EXL3 expert of the bank and is computed here;
-                              0: upstream behaviour, ids >= E are skipped (native/exl3.cu:151)             */
+                              0: upstream behaviour, ids >= E are skipped (native/exl3.cu:151);
+                              2: expert parallel, handles of <= 16 rows: decided per window on the device -- of the
+                                 ranks (equal contiguous expert windows, rank = expert_lo / window size) the one whose
+                                 window holds the fewest distinct routed experts of the routing table computes it
+                                 (ties: the lowest rank); every rank evaluates the same table, so all agree       */
     int32_t expert_lo;     /* expert-parallel window: of the routed experts only ids in [expert_lo,        */
     int32_t expert_hi;     /* expert_hi) are computed here (0, E = all of them)                            */
     float   limit;         /* SwiGLU clamp (upstream 10.0, src/experts.rs:521)                             */
@@ -232,7 +236,8 @@ void glmflash_ep_free(glmflash_ep *h);
 int  glmflash_ep_get_handle(glmflash_ep *h, void *handle_out);
 int  glmflash_ep_connect(glmflash_ep *h, const void *all_handles /* world x handle_bytes, rank order */);
 /* Y: fp32 [rows*slots][H] pair results of this rank (glmflash_moe_pairs); the config's expert window decides which
- * routed pairs are this rank's, shared_here whether the shared expert's pair is (it may move from layer to layer).
+ * routed pairs are this rank's, shared_here whether the shared expert's pair is (it may move from layer to layer):
+ * 1 / 0, or 2 = decided per window on the device by the rule of config.shared_exl3 = 2 (windows of <= 16 rows).
  * Result: glmflash_ep_output() fp32 [rows][H]. */
 int  glmflash_ep_combine(glmflash_ep *h, void *stream, const float *Y, const int32_t *picks, const float *route_w, int rows,
                          int shared_here);
@@ -242,7 +247,8 @@ float *glmflash_ep_output(const glmflash_ep *h);
  * the layer kernel stores each finished 128-column block of this rank's partial straight into every peer's receive slot
  * and adds the ranks' slots in rank order itself; otherwise, and for larger windows, the experts run and then
  * glmflash_ep_combine.  shared_here: 1 / 0 = this rank computes / skips the shared
- * expert in this call, -1 = as the layer owner's config says.  Result: glmflash_ep_output(). */
+ * expert in this call, 2 = decided per window on the device (the layer owner's config must say 2 as well), -1 = as the
+ * layer owner's config says.  Result: glmflash_ep_output(). */
 int  glmflash_moe_run_ep(glmflash_moe *m, glmflash_ep *ep, void *stream, const glmflash_weights *w, const void *input,
                          int x_stride, const int32_t *picks, const float *route_w, int rows, int shared_here);
 const int32_t *glmflash_ep_status(const glmflash_ep *h);

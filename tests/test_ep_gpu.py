@@ -37,8 +37,11 @@ def _worker(rank, world, port, rows_list, q):
         for rows, launches in [(r, k) for r in rows_list for k in ((3, 1) if r <= 16 else (3,))]:
             # launches = 1: the one-launch layer kernel with the exchange inside; 3: expert kernels, then the exchange kernel
             os.environ["GLMFLASH_LAYER_KERNELS"] = str(launches)
-            layer = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nvlink")
-            base = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nccl")
+            # three launches, windows of <= 16 rows: also with the shared expert's owner decided per window on the device
+            # (every second layer set); the one-launch kernel serves the round-robin rule only
+            dyn = launches == 3 and rows == 16
+            layer = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nvlink", dynamic_shared=dyn)
+            base = ep.EpMoe(pkg, rank, world, rows, H, I, E, S, device=dev, exchange="nccl", dynamic_shared=dyn)
             single = pkg.Moe(pkg.make_config(H, I, E, S, max_rows=rows))
             for l in range(2):
                 bank = synth.device_bank(300 + l, H, I, E, dev)

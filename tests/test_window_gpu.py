@@ -150,6 +150,54 @@ def test_eight_expert_windows_sum_to_the_layer(pkg, synth, cuda, banks, launches
     assert rel_err(total, full)[0] < 1e-5
 
 
+@pytest.mark.parametrize("rows", [1, 2, 7, 16])
+def test_shared_expert_owner_decided_per_window(pkg, synth, cuda, banks, rows):
+    """shared_exl3 = 2: of eight ranks the one whose expert window holds the fewest distinct routed experts of the window's
+    routing table (ties: the lowest rank) computes the shared expert.  Exactly that rank's partial contains it, the
+    partials add up to the layer, and the rank's local combine (the NCCL-baseline path) agrees with its expert kernels."""
+    _, dev = banks
+    x = synth.activations_bf16(171 + rows, rows, H)
+    picks, rw = synth.route(172 + rows, rows, E, S - 1, shared_bias=rows > 1)
+    full = _run(_moe(pkg, 3, hidden=H, inter=I, experts=E, slots=S, max_rows=16), dev["scaled"], x, picks, rw, rows, cuda)
+    loads = [len({int(e) for e in picks[:, :S - 1].ravel() if 8 * r <= e < 8 * r + 8}) for r in range(8)]
+    owner = min(range(8), key=lambda r: (loads[r], r))
+    total = np.zeros_like(full)
+    for r in range(8):
+        kw = dict(hidden=H, inter=I, experts=E, slots=S, max_rows=16, expert_lo=8 * r, expert_hi=8 * r + 8)
+        dyn = _run(_moe(pkg, 3, shared_exl3=2, **kw), dev["scaled"], x, picks, rw, rows, cuda)
+        fixed = _run(_moe(pkg, 3, shared_exl3=int(r == owner), **kw), dev["scaled"], x, picks, rw, rows, cuda)
+        assert (dyn.view(np.uint32) == fixed.view(np.uint32)).all(), (r, owner, loads)
+        total += dyn
+    assert rel_err(total, full)[0] < 1e-5
+
+
+def test_exchange_with_the_owner_decided_per_window_on_one_gpu(pkg, synth, cuda, banks):
+    """The three-launch pipeline + the flag-in-data exchange with shared_here = 2, two ranks emulated on one GPU as in the
+    test below: the expert kernels and the exchange kernel of a rank take the same decision, so the sum is the layer."""
+    import torch
+    _, dev = banks
+    for rows in (1, 6, 16):
+        x = synth.activations_bf16(191 + rows, rows, H)
+        picks, rw = synth.route(192 + rows, rows, E, S - 1, shared_bias=rows > 1)
+        full = _run(_moe(pkg, 3, hidden=H, inter=I, experts=E, slots=S, max_rows=16), dev["scaled"], x, picks, rw, rows, cuda)
+        kw = lambda r: dict(hidden=H, inter=I, experts=E, slots=S, max_rows=16, expert_lo=r * 32, expert_hi=(r + 1) * 32, shared_exl3=2)
+        moes = [_moe(pkg, 3, **kw(r)) for r in (0, 1)]
+        eps = [pkg.EpCombine(pkg.make_config(**kw(r)), r, 2, None) for r in (0, 1)]
+        for e_ in eps:
+            e_.connect_ptrs([q.local_base for q in eps])
+        xd, pd, wd = _bf16_dev(x, cuda), torch.from_numpy(picks).to(cuda), torch.from_numpy(rw).to(cuda)
+        eps[1].set_wait_limit(20000)
+        moes[1].run_ep(eps[1], dev["scaled"], xd, pd, wd, rows, shared_here=2)
+        torch.cuda.synchronize()
+        assert int(eps[1].status.cpu()[0]) == 4                 # rank 1 gave up waiting for rank 0: nothing hung
+        got = moes[0].run_ep(eps[0], dev["scaled"], xd, pd, wd, rows)          # -1: as the layer owner's config says (2)
+        torch.cuda.synchronize()
+        assert int(eps[0].status.cpu()[0]) == 0 and int(moes[0].status.cpu()[0]) == 0 and int(moes[1].status.cpu()[0]) == 0
+        assert rel_err(got.cpu().numpy(), full)[0] < 1e-5, rows
+        with pytest.raises(RuntimeError, match="decided per window"):
+            moes[0].run_ep(eps[0], dev["scaled"], xd, pd, wd, rows, shared_here=1)
+
+
 def test_small_and_odd_shapes_vs_oracle(pkg, oracle, synth, cuda):
     """Shapes other than the benchmark's: one split per projection, and a hidden size (2304) that is not a power of
     two times 256 (nine splits in the layer kernel, 6 x 24 k-tiles in the table-driven kernels)."""
