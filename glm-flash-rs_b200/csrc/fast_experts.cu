@@ -283,15 +283,26 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 
 // In-register 128-point Walsh-Hadamard transform, butterflies stride 1..64, (lower + upper, lower - upper):
 // upstream's order (native/exl3.cu:208-219), so every sum associates as there.
+// From stride 2 on, the two neighbours (i, i + 1) take the same side of their butterflies, so a pair goes through one
+// packed fp32 instruction of sm_100 (add.f32x2 / fma.f32x2; a - b as b * -1 + a, one rounding, the same bits): half
+// the issue slots of the transform, which matters because this kernel is bound by instruction issue.
 __device__ __forceinline__ void fwht128_regs(float (&v)[128]) {
 #pragma unroll
-    for (int s = 1; s < 128; s <<= 1)
+    for (int i = 0; i < 128; i += 2) {
+        const float a = v[i], b = v[i + 1];
+        v[i] = a + b;
+        v[i + 1] = a - b;
+    }
+    const float2 neg1 = make_float2(-1.f, -1.f);
 #pragma unroll
-        for (int i = 0; i < 128; ++i)
+    for (int s = 2; s < 128; s <<= 1)
+#pragma unroll
+        for (int i = 0; i < 128; i += 2)
             if (!(i & s)) {
-                const float a = v[i], b = v[i | s];
-                v[i] = a + b;
-                v[i | s] = a - b;
+                const float2 a = make_float2(v[i], v[i + 1]), b = make_float2(v[i | s], v[(i | s) + 1]);
+                const float2 lo = __fadd2_rn(a, b), hi = __ffma2_rn(b, neg1, a);
+                v[i] = lo.x; v[i + 1] = lo.y;
+                v[i | s] = hi.x; v[(i | s) + 1] = hi.y;
             }
 }
 
