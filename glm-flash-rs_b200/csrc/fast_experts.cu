@@ -283,6 +283,12 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t *bar, uint32_t parity, vo
 
 // In-register 128-point Walsh-Hadamard transform, butterflies stride 1..64, (lower + upper, lower - upper):
 // upstream's order (native/exl3.cu:208-219), so every sum associates as there.
+// Two values rounded to bf16 (nearest even) by one packed conversion, read back as fp32: per value the bits of bf16r.
+__device__ __forceinline__ float2 bf16r2(float x, float y) {
+    const __nv_bfloat162 b = __float22bfloat162_rn(make_float2(x, y));
+    const uint32_t w = *reinterpret_cast<const uint32_t *>(&b);
+    return make_float2(__uint_as_float(w << 16), __uint_as_float(w & 0xffff0000u));
+}
 // From stride 2 on, the two neighbours (i, i + 1) take the same side of their butterflies, so a pair goes through one
 // packed fp32 instruction of sm_100 (add.f32x2 / fma.f32x2; a - b as b * -1 + a, one rounding, the same bits): half
 // the issue slots of the transform, which matters because this kernel is bound by instruction issue.
@@ -529,20 +535,22 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                     // gate: scale, bf16 rounding, clamp, silu (rounded) -> two bf16 per word, this thread's column of gbuf
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
-                        const float g0 = fminf(bf16r(v[2 * i] * scales[2 * i]), a.limit);
-                        const float g1 = fminf(bf16r(v[2 * i + 1] * scales[2 * i + 1]), a.limit);
-                        const float s0 = bf16r(__fdividef(g0, 1.f + __expf(-g0)));
-                        const float s1 = bf16r(__fdividef(g1, 1.f + __expf(-g1)));
-                        gbuf[i * 256 + em] = (__float_as_uint(s0) >> 16) | (__float_as_uint(s1) & 0xffff0000u);
+                        const float2 gr = bf16r2(v[2 * i] * scales[2 * i], v[2 * i + 1] * scales[2 * i + 1]);
+                        const float g0 = fminf(gr.x, a.limit), g1 = fminf(gr.y, a.limit);
+                        // (one packed conversion rounds both values to bf16 and packs them: .x in the low half)
+                        const __nv_bfloat162 sp = __float22bfloat162_rn(make_float2(__fdividef(g0, 1.f + __expf(-g0)),
+                                                                                   __fdividef(g1, 1.f + __expf(-g1))));
+                        gbuf[i * 256 + em] = *reinterpret_cast<const uint32_t *>(&sp);
                     }
                 } else if (MATS == 2) {
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
                         const uint32_t gp = gbuf[i * 256 + em];
-                        const float u0 = fminf(fmaxf(bf16r(v[2 * i] * scales[128 + 2 * i]), -a.limit), a.limit);
-                        const float u1 = fminf(fmaxf(bf16r(v[2 * i + 1] * scales[128 + 2 * i + 1]), -a.limit), a.limit);
-                        v[2 * i] = bf16r(__uint_as_float(gp << 16) * u0) * scales[256 + 2 * i];
-                        v[2 * i + 1] = bf16r(__uint_as_float(gp & 0xffff0000u) * u1) * scales[256 + 2 * i + 1];
+                        const float2 ur = bf16r2(v[2 * i] * scales[128 + 2 * i], v[2 * i + 1] * scales[128 + 2 * i + 1]);
+                        const float u0 = fminf(fmaxf(ur.x, -a.limit), a.limit), u1 = fminf(fmaxf(ur.y, -a.limit), a.limit);
+                        const float2 pr = bf16r2(__uint_as_float(gp << 16) * u0, __uint_as_float(gp & 0xffff0000u) * u1);
+                        v[2 * i] = pr.x * scales[256 + 2 * i];
+                        v[2 * i + 1] = pr.y * scales[256 + 2 * i + 1];
                     }
                     fwht128_regs(v);
                     if (m < cnt) {
