@@ -531,11 +531,13 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                     continue;
                 }
                 fwht128_regs(v);
+                const float2 *sc2 = reinterpret_cast<const float2 *>(scales);       // (8-byte aligned: the tables are 128-byte aligned)
                 if (MATS == 2 && pm == 0) {
                     // gate: scale, bf16 rounding, clamp, silu (rounded) -> two bf16 per word, this thread's column of gbuf
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
-                        const float2 gr = bf16r2(v[2 * i] * scales[2 * i], v[2 * i + 1] * scales[2 * i + 1]);
+                        const float2 sg = sc2[i];
+                        const float2 gr = bf16r2(v[2 * i] * sg.x, v[2 * i + 1] * sg.y);
                         const float g0 = fminf(gr.x, a.limit), g1 = fminf(gr.y, a.limit);
                         // (one packed conversion rounds both values to bf16 and packs them: .x in the low half)
                         const __nv_bfloat162 sp = __float22bfloat162_rn(make_float2(__fdividef(g0, 1.f + __expf(-g0)),
@@ -546,11 +548,12 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
 #pragma unroll
                     for (int i = 0; i < 64; ++i) {
                         const uint32_t gp = gbuf[i * 256 + em];
-                        const float2 ur = bf16r2(v[2 * i] * scales[128 + 2 * i], v[2 * i + 1] * scales[128 + 2 * i + 1]);
+                        const float2 su = sc2[64 + i], sd2 = sc2[128 + i];
+                        const float2 ur = bf16r2(v[2 * i] * su.x, v[2 * i + 1] * su.y);
                         const float u0 = fminf(fmaxf(ur.x, -a.limit), a.limit), u1 = fminf(fmaxf(ur.y, -a.limit), a.limit);
                         const float2 pr = bf16r2(__uint_as_float(gp << 16) * u0, __uint_as_float(gp & 0xffff0000u) * u1);
-                        v[2 * i] = pr.x * scales[256 + 2 * i];
-                        v[2 * i + 1] = pr.y * scales[256 + 2 * i + 1];
+                        v[2 * i] = pr.x * sd2.x;
+                        v[2 * i + 1] = pr.y * sd2.y;
                     }
                     fwht128_regs(v);
                     if (m < cnt) {
@@ -559,8 +562,8 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
                         for (int c = 0; c < 16; ++c) {
                             __half2 h[4];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j)
-                                h[j] = __halves2half2(__float2half_rn(v[8 * c + 2 * j]), __float2half_rn(v[8 * c + 2 * j + 1]));
+                            for (int j = 0; j < 4; ++j)       // one packed conversion per pair (the same rounding per value)
+                                h[j] = __float22half2_rn(make_float2(v[8 * c + 2 * j], v[8 * c + 2 * j + 1]));
                             o[c] = make_uint4(*reinterpret_cast<uint32_t *>(&h[0]), *reinterpret_cast<uint32_t *>(&h[1]),
                                               *reinterpret_cast<uint32_t *>(&h[2]), *reinterpret_cast<uint32_t *>(&h[3]));
                         }
@@ -577,9 +580,9 @@ fast_gemm_kernel(const __grid_constant__ CUtensorMap mapA0, const __grid_constan
 #pragma unroll
                         for (int c = 0; c < 4; ++c) {
                             const int col = ch * 16 + 4 * c;
+                            const float4 s4 = *reinterpret_cast<const float4 *>(scales + col);
                             *reinterpret_cast<float4 *>(wbuf + lane * 16 + ((c ^ ((lane >> 1) & 3)) << 2)) =
-                                make_float4(v[col] * scales[col], v[col + 1] * scales[col + 1], v[col + 2] * scales[col + 2],
-                                            v[col + 3] * scales[col + 3]);
+                                make_float4(v[col] * s4.x, v[col + 1] * s4.y, v[col + 2] * s4.z, v[col + 3] * s4.w);
                         }
                         __syncwarp();
 #pragma unroll
